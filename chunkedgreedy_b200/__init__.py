@@ -1,0 +1,266 @@
+"""B200-native Chunked Greedy (csg) reordering, permutation application and SpMM.
+
+The compute entry points keep the keyword surface of the reference's Python
+package (sporder/python/sporder/__init__.py:113-149 ``reorder`` and :380-424
+``chunk_similarity_greedy``): same argument names and meaning, same return
+shapes (a bare array, or a tuple with ``timing`` and/or ``stats`` appended when
+requested), permutations in new2old form.  Use it as
+``import chunkedgreedy_b200 as sporder``.
+
+Arrays are CUDA tensors (``torch.Tensor``) or any object that exports DLPack /
+``__cuda_array_interface__``; results come back as torch tensors on the same
+device.  All work is done by hand-written sm_100a kernels behind the C ABI in
+``include/sporder_b200.h``; there is no CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+from . import _lib
+
+__all__ = ["Context", "chunk_similarity_greedy", "reorder", "spmm", "csg_table",
+           "chunk_similarity_greedy_host", "kernel_launches"]
+
+_default_ctx = {}
+
+
+def _torch():
+    import torch
+    return torch
+
+
+class Context:
+    """Owns a CUDA stream and a device workspace, bound to the device current at
+    creation (sporder/include/sporder.h:43-52).  One context per thread or device."""
+
+    def __init__(self):
+        torch = _torch()
+        if not torch.cuda.is_available():
+            raise RuntimeError("chunkedgreedy_b200 needs a CUDA device (no CPU fallback)")
+        lib = _lib.load()
+        torch.cuda.init()
+        self.device = torch.cuda.current_device()
+        # make sure the primary context exists before the library asks for the device
+        torch.empty(1, device="cuda")
+        self._h = lib.sporder_context_create()
+        if not self._h:
+            _lib.check()
+            raise RuntimeError("sporder_context_create failed")
+
+    @property
+    def handle(self):
+        return self._h
+
+    def workspace_bytes(self):
+        return int(_lib.load().sporder_context_workspace_bytes(self._h))
+
+    def close(self):
+        if getattr(self, "_h", None):
+            _lib.load().sporder_context_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _ctx(ctx):
+    if ctx is not None:
+        return ctx
+    torch = _torch()
+    dev = torch.cuda.current_device()
+    if dev not in _default_ctx:  # shared default context, created on first use
+        _default_ctx[dev] = Context()
+    return _default_ctx[dev]
+
+
+def _as_tensor(a, dtype, name):
+    torch = _torch()
+    if not isinstance(a, torch.Tensor):
+        a = torch.from_dlpack(a) if hasattr(a, "__dlpack__") else torch.as_tensor(a, device="cuda")
+    if not a.is_cuda:
+        raise ValueError("%s must be a CUDA array" % name)
+    if a.dtype != dtype:
+        raise ValueError("%s must have dtype %s (got %s)" % (name, dtype, a.dtype))
+    if a.dim() != 1:
+        raise ValueError("%s must be one-dimensional" % name)
+    return a.contiguous()
+
+
+def _enter(ctx, ref):
+    """Bind the context to the caller's current stream so that work queued by the
+    caller before the call is ordered before ours."""
+    torch = _torch()
+    stream = torch.cuda.current_stream(ref.device)
+    _lib.load().sporder_context_set_stream(ctx.handle, C.c_void_p(stream.cuda_stream))
+
+
+def _sizes(ptr, ind):
+    if ptr.numel() < 2:
+        raise ValueError("ptr must have length n+1 (at least 2)")
+    n, nnz = ptr.numel() - 1, ind.numel()
+    if n > 2**31 - 1 or nnz > 2**31 - 1:
+        raise ValueError("matrix too large for int32 indexing")
+    return n, nnz
+
+
+def _timing_dict(t):
+    return {"wall_ms": t.wall_ms, "csr2csc_ms": t.csr2csc_ms, "similarity_ms": t.similarity_ms,
+            "chunk_greedy_ms": t.chunk_greedy_ms}
+
+
+def _stats_dict(s):
+    return {f: getattr(s, f) for f, _ in s._fields_}
+
+
+def chunk_similarity_greedy(ptr, ind, *, is_symmetric=False, k=0, oversampling=0.0, chunk_size=0,
+                            with_timing=False, with_stats=False, ctx=None):
+    """One-shot per-chunk similarity + greedy seriation
+    (sporder/python/sporder/__init__.py:380-424).
+
+    Returns ``new_order`` (int32 CUDA tensor, new2old); a ``timing`` dict (wall_ms,
+    csr2csc_ms, similarity_ms, chunk_greedy_ms) and/or a ``stats`` dict (k_used, m_used,
+    avg_degree, avg_edge_weight, zero_degree_rows, chunk_size_used, chain_restarts,
+    avg_followed_weight) are appended when requested."""
+    torch = _torch()
+    ptr = _as_tensor(ptr, torch.int32, "ptr")
+    ind = _as_tensor(ind, torch.int32, "ind")
+    n, nnz = _sizes(ptr, ind)
+    ctx = _ctx(ctx)
+    lib = _lib.load()
+    with torch.cuda.device(ptr.device):
+        _enter(ctx, ptr)
+        order = torch.empty(n, dtype=torch.int32, device=ptr.device)
+        timing, stats = _lib.CsgTiming(), _lib.CsgStats()
+        lib.sporder_chunk_similarity_greedy(
+            ctx.handle, n, nnz, ptr.data_ptr(), ind.data_ptr(), bool(is_symmetric), int(k),
+            float(oversampling), int(chunk_size), order.data_ptr(),
+            C.byref(timing) if with_timing else None, C.byref(stats) if with_stats else None)
+    msg = _lib.last_error()
+    if msg:
+        raise ValueError(msg) if "expect" in msg or "must be" in msg else RuntimeError(msg)
+    result = (order,)
+    if with_timing:
+        result += (_timing_dict(timing),)
+    if with_stats:
+        result += (_stats_dict(stats),)
+    return result if len(result) > 1 else result[0]
+
+
+def csg_table(ptr, ind, *, is_symmetric=False, k=0, oversampling=0.0, chunk_size=0,
+              with_order=True, ctx=None):
+    """csg that also returns the top-k candidate table: ``(order, table)`` with
+    ``table`` an ``(n, k_used)`` int64 tensor of packed entries (high word = fp32 bits
+    of the weight, low word = index + 1, 0 = empty).  No reference counterpart: the
+    reference never exposes this table."""
+    torch = _torch()
+    ptr = _as_tensor(ptr, torch.int32, "ptr")
+    ind = _as_tensor(ind, torch.int32, "ind")
+    n, nnz = _sizes(ptr, ind)
+    ctx = _ctx(ctx)
+    lib = _lib.load()
+    kk = int(k) if k > 0 else min(256, max(16, nnz // n))
+    with torch.cuda.device(ptr.device):
+        _enter(ctx, ptr)
+        order = torch.empty(n, dtype=torch.int32, device=ptr.device) if with_order else None
+        table = torch.empty((n, kk), dtype=torch.int64, device=ptr.device)
+        k_used = lib.sporder_csg_with_table(
+            ctx.handle, n, nnz, ptr.data_ptr(), ind.data_ptr(), bool(is_symmetric), int(k),
+            float(oversampling), int(chunk_size), order.data_ptr() if with_order else None,
+            table.data_ptr(), table.numel(), None, None)
+    msg = _lib.last_error()
+    if msg:
+        raise ValueError(msg) if "expect" in msg or "must be" in msg else RuntimeError(msg)
+    assert k_used == kk
+    return order, table
+
+
+def chunk_similarity_greedy_host(ptr, ind, *, is_symmetric=False, k=0, oversampling=0.0,
+                                 chunk_size=0, out=None, ctx=None):
+    """csg on HOST int32 tensors (pinned for full copy speed): copies the pattern to
+    the device, reorders, copies the permutation back into ``out`` (a host int32
+    tensor, allocated pinned when None).  No reference counterpart."""
+    torch = _torch()
+    if ptr.is_cuda or ind.is_cuda or ptr.dtype != torch.int32 or ind.dtype != torch.int32:
+        raise ValueError("ptr and ind must be int32 host tensors")
+    n, nnz = _sizes(ptr, ind)
+    ctx = _ctx(ctx)
+    if out is None:
+        out = torch.empty(n, dtype=torch.int32).pin_memory()
+    lib = _lib.load()
+    lib.sporder_context_set_stream(ctx.handle, None)
+    rc = lib.sporder_chunk_similarity_greedy_host(
+        ctx.handle, n, nnz, ptr.data_ptr(), ind.data_ptr(), bool(is_symmetric), int(k),
+        float(oversampling), int(chunk_size), out.data_ptr(), None, None)
+    if rc != 0:
+        _lib.check()
+    return out
+
+
+def reorder(ptr, ind, new_order, *, val=None, symmetric=False, ctx=None):
+    """Apply a row (or symmetric row+column) permutation to a CSR pattern
+    (sporder/python/sporder/__init__.py:113-149).  Returns ``(ptr_new, ind_new)`` or
+    ``(ptr_new, ind_new, val_new)``; column indices are sorted inside each row."""
+    torch = _torch()
+    ptr = _as_tensor(ptr, torch.int32, "ptr")
+    ind = _as_tensor(ind, torch.int32, "ind")
+    new_order = _as_tensor(new_order, torch.int32, "new_order")
+    n, nnz = _sizes(ptr, ind)
+    if new_order.numel() != n:
+        raise ValueError("new_order must have length n")
+    if val is not None:
+        val = _as_tensor(val, torch.float32, "val")
+        if val.device != ptr.device:
+            raise ValueError("val must live on the same device as ptr")
+        if val.numel() != nnz:
+            raise ValueError("val must have length nnz")
+    ctx = _ctx(ctx)
+    lib = _lib.load()
+    with torch.cuda.device(ptr.device):
+        _enter(ctx, ptr)
+        ptr_new = torch.empty(n + 1, dtype=torch.int32, device=ptr.device)
+        ind_new = torch.empty(max(nnz, 1), dtype=torch.int32, device=ptr.device)[:nnz]
+        val_new = None
+        if val is not None:
+            val_new = torch.empty(max(nnz, 1), dtype=torch.float32, device=ptr.device)[:nnz]
+        lib.sporder_reorder(ctx.handle, n, nnz, ptr.data_ptr(), ind.data_ptr(),
+                            val.data_ptr() if val is not None else None, new_order.data_ptr(),
+                            1 if symmetric else 0, ptr_new.data_ptr(), ind_new.data_ptr(),
+                            val_new.data_ptr() if val is not None else None)
+    _lib.check()
+    return (ptr_new, ind_new) if val is None else (ptr_new, ind_new, val_new)
+
+
+def spmm(ptr, ind, val, B, *, out=None, sync=True, ctx=None):
+    """fp32 CSR SpMM ``C = A @ B`` with ``B`` a row-major ``(n, w)`` float32 CUDA
+    tensor.  The reference has no first-party SpMM (it times third-party kernels,
+    bench/spmm/spmm_bench/base.py:48-59); this is the kernel the reordered matrix is
+    fed to.  ``sync=False`` skips the final stream synchronisation."""
+    torch = _torch()
+    ptr = _as_tensor(ptr, torch.int32, "ptr")
+    ind = _as_tensor(ind, torch.int32, "ind")
+    val = _as_tensor(val, torch.float32, "val")
+    n, nnz = _sizes(ptr, ind)
+    if B.dim() != 2 or B.shape[0] != n or B.dtype != torch.float32 or not B.is_cuda:
+        raise ValueError("B must be a float32 CUDA tensor of shape (n, w)")
+    B = B.contiguous()
+    w = B.shape[1]
+    ctx = _ctx(ctx)
+    lib = _lib.load()
+    with torch.cuda.device(ptr.device):
+        _enter(ctx, ptr)
+        if out is None:
+            out = torch.empty((n, w), dtype=torch.float32, device=ptr.device)
+        fn = lib.sporder_spmm if sync else lib.sporder_spmm_async
+        rc = fn(ctx.handle, n, nnz, w, ptr.data_ptr(), ind.data_ptr(), val.data_ptr(),
+                B.data_ptr(), out.data_ptr())
+    if rc != 0:
+        _lib.check()
+    return out
+
+
+def kernel_launches():
+    """Kernels launched by the library in this process so far."""
+    return int(_lib.load().sporder_kernel_launches())

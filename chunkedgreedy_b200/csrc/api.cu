@@ -1,0 +1,382 @@
+// C ABI of the library (include/sporder_b200.h): context, parameter resolution,
+// the csg pipeline driver and the thin wrappers around reorder and SpMM.
+#include "../../include/sporder_b200.h"
+
+#include <atomic>
+#include <chrono>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace csg {
+
+// ---- error channel ---------------------------------------------------------
+namespace {
+thread_local char g_err[512];
+thread_local bool g_has_err = false;
+std::atomic<uint64_t> g_launches{0};
+}  // namespace
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  g_has_err = true;
+}
+bool has_error() { return g_has_err; }
+static void clear_error() { g_has_err = false; }
+void count_launches(int k) { g_launches.fetch_add(static_cast<uint64_t>(k), std::memory_order_relaxed); }
+
+bool ensure_workspace(Context &ctx, size_t bytes) {
+  if (bytes <= ctx.ws_bytes) return true;
+  CSG_CUDA(cudaStreamSynchronize(ctx.stream));
+  if (ctx.ws) CSG_CUDA(cudaFree(ctx.ws));
+  ctx.ws = nullptr;
+  ctx.ws_bytes = 0;
+  const size_t want = bytes + (bytes >> 3);  // head room so that similar sizes reuse it
+  cudaError_t e = cudaMalloc(&ctx.ws, want);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    e = cudaMalloc(&ctx.ws, bytes);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      set_error("device workspace of %zu bytes: %s", bytes, cudaGetErrorString(e));
+      return false;
+    }
+    ctx.ws_bytes = bytes;
+    return true;
+  }
+  ctx.ws_bytes = want;
+  return true;
+}
+
+// sporder/src/sporder.cpp:147-161 and the checks of
+// sporder/src/common/chunk_similarity_top_k.cu:143-147
+bool resolve_params(int32_t n, int32_t nnz, int32_t k, float ovs, int32_t chunk, CsgParams *out) {
+  CSG_REQUIRE(n >= 1, "n must be >= 1 (got %d)", n);
+  CSG_REQUIRE(nnz >= 0, "nnz must be >= 0 (got %d)", nnz);
+  if (k <= 0) {
+    int32_t a = nnz / n;
+    if (a < 16) a = 16;
+    if (a > 256) a = 256;
+    k = a;
+  }
+  if (ovs <= 0.0f) ovs = 4.0f;
+  if (chunk <= 0) chunk = 1024;
+  const int32_t m = static_cast<int32_t>(static_cast<float>(k) * ovs);
+  out->k = k;
+  out->ovs = ovs;
+  out->chunk = chunk;
+  out->m_used = ((m + 31) / 32) * 32;
+  CSG_REQUIRE(ovs >= 1.0f, "expect oversampling >= 1 (got %g)", static_cast<double>(ovs));
+  CSG_REQUIRE(m <= 512, "expect k * oversampling <= 512 (got %d)", m);
+  const int32_t mm = m < 1 ? 1 : m;
+  out->M = ((mm + 31) / 32) * 32;
+  return true;
+}
+
+namespace {
+
+struct ChainStatsHost {
+  unsigned long long total_degree;
+  double total_weight;
+  double link_weight_sum;
+  int32_t zero_degree_rows;
+  int32_t restarts;
+  int32_t links;
+  int32_t pad;
+};
+
+size_t greedy_bitmap_words(int32_t n, int32_t chunk) {
+  const int32_t span = chunk < n ? chunk : n;
+  const size_t words = (static_cast<size_t>(span) + 31) / 32;
+  if (4 /*warps*/ * 2 * words * sizeof(uint32_t) <= 48 * 1024) return 0;
+  const size_t chunks = (static_cast<size_t>(n) + chunk - 1) / chunk;
+  return chunks * 2 * words;
+}
+
+// Lays out the scratch of one csg call in the context workspace.
+bool plan_scratch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, uint64_t *user_table,
+                  CsgScratch *s) {
+  Arena ar;
+  const size_t z = static_cast<size_t>(nnz > 0 ? nnz : 1);
+  const size_t o_keyA = ar.take(4 * z), o_keyB = ar.take(4 * z);
+  const size_t o_payA = ar.take(4 * z), o_payB = ar.take(4 * z);
+  const size_t o_cand = ar.take(8 * z), o_seg = ar.take(8 * z);
+  const size_t o_work = ar.take(4 * static_cast<size_t>(n));
+  const size_t o_list = ar.take(4 * static_cast<size_t>(n));
+  const size_t o_ctrl = ar.take(4 * CTRL_WORDS);
+  const size_t bw = greedy_bitmap_words(n, p.chunk);
+  const size_t o_bm = ar.take(4 * (bw ? bw : 1));
+  const size_t o_table = user_table ? 0 : ar.take(8 * static_cast<size_t>(n) * p.k);
+  if (!ensure_workspace(ctx, ar.off)) return false;
+  s->keyA = reinterpret_cast<uint32_t *>(ctx.ws + o_keyA);
+  s->keyB = reinterpret_cast<uint32_t *>(ctx.ws + o_keyB);
+  s->payA = reinterpret_cast<uint32_t *>(ctx.ws + o_payA);
+  s->payB = reinterpret_cast<uint32_t *>(ctx.ws + o_payB);
+  s->cand = reinterpret_cast<int2 *>(ctx.ws + o_cand);
+  s->seg = reinterpret_cast<int2 *>(ctx.ws + o_seg);
+  s->row_work = reinterpret_cast<uint32_t *>(ctx.ws + o_work);
+  s->row_list = reinterpret_cast<int32_t *>(ctx.ws + o_list);
+  s->ctrl = reinterpret_cast<uint32_t *>(ctx.ws + o_ctrl);
+  s->table = user_table ? user_table : reinterpret_cast<uint64_t *>(ctx.ws + o_table);
+  s->gbitmaps = bw ? reinterpret_cast<uint32_t *>(ctx.ws + o_bm) : nullptr;
+  return true;
+}
+
+// The pipeline of sporder/src/csg/chunk_similarity_greedy.cu:100-138 with the
+// stages of this library: chunk-local transpose -> sketch/top-k -> greedy.
+bool run_csg(Context &ctx, int32_t n, int32_t nnz, const int32_t *d_ptr, const int32_t *d_ind,
+             int32_t k, float ovs, int32_t chunk, int32_t *d_new_order, uint64_t *d_table,
+             uint64_t table_capacity, sporder_csg_timing_t *timing, sporder_csg_stats_t *stats,
+             int32_t *k_used) {
+  const auto wall0 = std::chrono::steady_clock::now();
+  CsgParams p;
+  if (!resolve_params(n, nnz, k, ovs, chunk, &p)) return false;
+  if (k_used) *k_used = p.k;
+  if (stats) {
+    std::memset(stats, 0, sizeof(*stats));
+    stats->k_used = p.k;
+    stats->m_used = p.m_used;
+    stats->chunk_size_used = p.chunk;
+  }
+  CSG_REQUIRE(d_ptr && (d_ind || nnz == 0), "null CSR arrays");
+  CSG_REQUIRE(!d_table || table_capacity >= static_cast<uint64_t>(n) * p.k,
+              "table buffer holds %llu entries, need n * k = %llu",
+              static_cast<unsigned long long>(table_capacity),
+              static_cast<unsigned long long>(static_cast<uint64_t>(n) * p.k));
+  CSG_CUDA(cudaSetDevice(ctx.device));
+  CsgScratch s;
+  if (!plan_scratch(ctx, n, nnz, p, d_table, &s)) return false;
+  cudaStream_t st = ctx.stream;
+
+  if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[0], st));
+  if (!launch_transpose(ctx, n, nnz, p.chunk, d_ptr, d_ind, s)) return false;
+  if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
+  if (!launch_sketch(ctx, n, p, d_ptr, s)) return false;
+  if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[2], st));
+  if (stats && !launch_table_stats(ctx, n, p.k, s.table, s.ctrl)) return false;
+  if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[3], st));
+  if (d_new_order) {
+    if (!launch_greedy(ctx, n, p, s, d_new_order, stats != nullptr)) return false;
+  }
+  if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[4], st));
+  ChainStatsHost hs;
+  if (stats)
+    CSG_CUDA(cudaMemcpyAsync(&hs, s.ctrl + CTRL_STATS, sizeof(hs), cudaMemcpyDeviceToHost, st));
+  CSG_CUDA(cudaStreamSynchronize(st));
+  CSG_CUDA(cudaGetLastError());
+  if (stats) {  // sporder/src/csg/stats_collector.cu:53-62
+    stats->avg_degree = static_cast<double>(hs.total_degree) / n;
+    stats->avg_edge_weight =
+        hs.total_degree > 0 ? hs.total_weight / static_cast<double>(hs.total_degree) : 0.0;
+    stats->zero_degree_rows = hs.zero_degree_rows;
+    stats->chain_restarts = hs.restarts;
+    stats->avg_followed_weight = hs.links > 0 ? hs.link_weight_sum / hs.links : 0.0;
+  }
+  if (timing) {
+    CSG_CUDA(cudaEventElapsedTime(&timing->csr2csc_ms, ctx.ev[0], ctx.ev[1]));
+    CSG_CUDA(cudaEventElapsedTime(&timing->similarity_ms, ctx.ev[1], ctx.ev[2]));
+    CSG_CUDA(cudaEventElapsedTime(&timing->chunk_greedy_ms, ctx.ev[3], ctx.ev[4]));
+    timing->wall_ms =
+        std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - wall0).count();
+  }
+  return true;
+}
+
+}  // namespace
+}  // namespace csg
+
+struct sporder_context_struct {
+  csg::Context c;
+};
+
+extern "C" {
+
+sporder_context_t sporder_context_create(void) {
+  csg::clear_error();
+  auto *h = new sporder_context_struct;
+  csg::Context &c = h->c;
+  auto fail = [&](cudaError_t e, const char *what) {
+    csg::set_error("context: %s -> %s", what, cudaGetErrorString(e));
+    delete h;
+    return static_cast<sporder_context_t>(nullptr);
+  };
+  cudaError_t e;
+  if ((e = cudaGetDevice(&c.device)) != cudaSuccess) return fail(e, "cudaGetDevice");
+  if ((e = cudaStreamCreateWithFlags(&c.own_stream, cudaStreamNonBlocking)) != cudaSuccess)
+    return fail(e, "cudaStreamCreate");
+  c.stream = c.own_stream;
+  cudaDeviceGetAttribute(&c.num_sms, cudaDevAttrMultiProcessorCount, c.device);
+  cudaDeviceGetAttribute(&c.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, c.device);
+  for (auto &ev : c.ev)
+    if ((e = cudaEventCreate(&ev)) != cudaSuccess) return fail(e, "cudaEventCreate");
+  if ((e = cudaMallocHost(&c.h_pinned, 64 * sizeof(int))) != cudaSuccess)
+    return fail(e, "cudaMallocHost");
+  return h;
+}
+
+void sporder_context_destroy(sporder_context_t h) {
+  if (!h) return;
+  csg::Context &c = h->c;
+  cudaSetDevice(c.device);
+  cudaStreamSynchronize(c.stream);
+  if (c.ws) cudaFree(c.ws);
+  for (auto &ev : c.ev)
+    if (ev) cudaEventDestroy(ev);
+  if (c.h_pinned) cudaFreeHost(c.h_pinned);
+  if (c.own_stream) cudaStreamDestroy(c.own_stream);
+  delete h;
+}
+
+void sporder_context_set_stream(sporder_context_t h, void *stream) {
+  if (!h) return;
+  h->c.stream = stream ? static_cast<cudaStream_t>(stream) : h->c.own_stream;
+}
+
+uint64_t sporder_context_workspace_bytes(sporder_context_t h) { return h ? h->c.ws_bytes : 0; }
+
+const char *sporder_last_error(void) { return csg::g_has_err ? csg::g_err : nullptr; }
+
+uint64_t sporder_kernel_launches(void) { return csg::g_launches.load(); }
+
+void sporder_chunk_similarity_greedy(sporder_context_t ctx, int32_t n, int32_t nnz,
+                                     const int32_t *d_ptr, const int32_t *d_ind, bool is_symmetric,
+                                     int32_t k, float oversampling, int32_t chunk_size,
+                                     int32_t *d_new_order, sporder_csg_timing_t *timing,
+                                     sporder_csg_stats_t *stats) {
+  (void)is_symmetric;
+  csg::clear_error();
+  if (!ctx) {
+    csg::set_error("null context");
+    return;
+  }
+  if (!d_new_order) {
+    csg::set_error("null d_new_order");
+    return;
+  }
+  csg::run_csg(ctx->c, n, nnz, d_ptr, d_ind, k, oversampling, chunk_size, d_new_order, nullptr, 0,
+               timing, stats, nullptr);
+}
+
+int32_t sporder_csg_with_table(sporder_context_t ctx, int32_t n, int32_t nnz, const int32_t *d_ptr,
+                               const int32_t *d_ind, bool is_symmetric, int32_t k,
+                               float oversampling, int32_t chunk_size, int32_t *d_new_order,
+                               uint64_t *d_table, uint64_t d_table_capacity,
+                               sporder_csg_timing_t *timing, sporder_csg_stats_t *stats) {
+  (void)is_symmetric;
+  csg::clear_error();
+  if (!ctx) {
+    csg::set_error("null context");
+    return -1;
+  }
+  int32_t k_used = -1;
+  if (!csg::run_csg(ctx->c, n, nnz, d_ptr, d_ind, k, oversampling, chunk_size, d_new_order, d_table,
+                    d_table_capacity, timing, stats, &k_used))
+    return -1;
+  return k_used;
+}
+
+int32_t sporder_chunk_similarity_greedy_host(sporder_context_t ctx, int32_t n, int32_t nnz,
+                                             const int32_t *h_ptr, const int32_t *h_ind,
+                                             bool is_symmetric, int32_t k, float oversampling,
+                                             int32_t chunk_size, int32_t *h_new_order,
+                                             sporder_csg_timing_t *timing,
+                                             sporder_csg_stats_t *stats) {
+  (void)is_symmetric;
+  csg::clear_error();
+  if (!ctx || !h_ptr || !h_new_order || n < 1 || nnz < 0) {
+    csg::set_error("csg_host: bad arguments");
+    return -1;
+  }
+  csg::Context &c = ctx->c;
+  auto run = [&]() -> bool {
+    CSG_CUDA(cudaSetDevice(c.device));
+    // staging buffers of the host entry point live outside the workspace cache
+    int32_t *d_ptr = nullptr, *d_ind = nullptr, *d_order = nullptr;
+    CSG_CUDA(cudaMallocAsync(&d_ptr, sizeof(int32_t) * (static_cast<size_t>(n) + 1), c.stream));
+    CSG_CUDA(cudaMallocAsync(&d_ind, sizeof(int32_t) * static_cast<size_t>(nnz > 0 ? nnz : 1), c.stream));
+    CSG_CUDA(cudaMallocAsync(&d_order, sizeof(int32_t) * static_cast<size_t>(n), c.stream));
+    CSG_CUDA(cudaMemcpyAsync(d_ptr, h_ptr, sizeof(int32_t) * (static_cast<size_t>(n) + 1),
+                             cudaMemcpyHostToDevice, c.stream));
+    if (nnz > 0)
+      CSG_CUDA(cudaMemcpyAsync(d_ind, h_ind, sizeof(int32_t) * static_cast<size_t>(nnz),
+                               cudaMemcpyHostToDevice, c.stream));
+    const bool ok = csg::run_csg(c, n, nnz, d_ptr, d_ind, k, oversampling, chunk_size, d_order,
+                                 nullptr, 0, timing, stats, nullptr);
+    if (ok)
+      CSG_CUDA(cudaMemcpyAsync(h_new_order, d_order, sizeof(int32_t) * static_cast<size_t>(n),
+                               cudaMemcpyDeviceToHost, c.stream));
+    cudaFreeAsync(d_ptr, c.stream);
+    cudaFreeAsync(d_ind, c.stream);
+    cudaFreeAsync(d_order, c.stream);
+    CSG_CUDA(cudaStreamSynchronize(c.stream));
+    return ok;
+  };
+  return run() ? 0 : -1;
+}
+
+void sporder_reorder(sporder_context_t ctx, int32_t n, int32_t nnz, const int32_t *d_ptr_old,
+                     const int32_t *d_ind_old, const float *d_val_old, const int32_t *d_new_order,
+                     sporder_reorder_mode_t mode, int32_t *d_ptr_new, int32_t *d_ind_new,
+                     float *d_val_new) {
+  csg::clear_error();
+  if (!ctx) {
+    csg::set_error("null context");
+    return;
+  }
+  if (mode != SPORDER_REORDER_ROWS && mode != SPORDER_REORDER_SYMMETRIC) {
+    csg::set_error("invalid reorder mode");
+    return;
+  }
+  if (n < 1 || nnz < 0 || !d_ptr_old || !d_new_order || !d_ptr_new || (nnz > 0 && (!d_ind_old || !d_ind_new))) {
+    csg::set_error("reorder: bad arguments");
+    return;
+  }
+  csg::Context &c = ctx->c;
+  auto run = [&]() -> bool {
+    CSG_CUDA(cudaSetDevice(c.device));
+    if (!csg::launch_reorder(c, n, nnz, d_ptr_old, d_ind_old, d_val_old, d_new_order,
+                             static_cast<int>(mode), d_ptr_new, d_ind_new, d_val_new))
+      return false;
+    CSG_CUDA(cudaStreamSynchronize(c.stream));
+    CSG_CUDA(cudaGetLastError());
+    return true;
+  };
+  run();
+}
+
+static int32_t spmm_impl(sporder_context_t ctx, int32_t n, int32_t nnz, int32_t w,
+                         const int32_t *d_ptr, const int32_t *d_ind, const float *d_val,
+                         const float *d_B, float *d_C, bool sync) {
+  csg::clear_error();
+  if (!ctx || n < 1 || nnz < 0 || !d_ptr || !d_B || !d_C || (nnz > 0 && (!d_ind || !d_val))) {
+    csg::set_error("spmm: bad arguments");
+    return -1;
+  }
+  csg::Context &c = ctx->c;
+  auto run = [&]() -> bool {
+    CSG_CUDA(cudaSetDevice(c.device));
+    if (!csg::launch_spmm(c, n, nnz, w, d_ptr, d_ind, d_val, d_B, d_C)) return false;
+    if (sync) {
+      CSG_CUDA(cudaStreamSynchronize(c.stream));
+      CSG_CUDA(cudaGetLastError());
+    }
+    return true;
+  };
+  return run() ? 0 : -1;
+}
+
+int32_t sporder_spmm(sporder_context_t ctx, int32_t n, int32_t nnz, int32_t w, const int32_t *d_ptr,
+                     const int32_t *d_ind, const float *d_val, const float *d_B, float *d_C) {
+  return spmm_impl(ctx, n, nnz, w, d_ptr, d_ind, d_val, d_B, d_C, true);
+}
+
+int32_t sporder_spmm_async(sporder_context_t ctx, int32_t n, int32_t nnz, int32_t w,
+                           const int32_t *d_ptr, const int32_t *d_ind, const float *d_val,
+                           const float *d_B, float *d_C) {
+  return spmm_impl(ctx, n, nnz, w, d_ptr, d_ind, d_val, d_B, d_C, false);
+}
+
+}  // extern "C"

@@ -1,0 +1,136 @@
+// Shared declarations of the B200 csg library: context, error channel,
+// workspace arena and the launch functions of each stage.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+namespace csg {
+
+// ---- error channel -------------------------------------------------------
+// The reference aborts the process on invalid arguments and CUDA errors
+// (sporder/src/common/error_checking.h:20-29).  On a shared GPU pool this
+// library records the message per thread and returns instead.
+void set_error(const char *fmt, ...);
+bool has_error();
+void count_launches(int k);  // feeds sporder_kernel_launches()
+
+#define CSG_CUDA(call)                                                                  \
+  do {                                                                                  \
+    cudaError_t e__ = (call);                                                           \
+    if (e__ != cudaSuccess) {                                                           \
+      ::csg::set_error("%s:%d: %s -> %s", __FILE__, __LINE__, #call,                    \
+                       cudaGetErrorString(e__));                                        \
+      return false;                                                                     \
+    }                                                                                   \
+  } while (0)
+
+#define CSG_REQUIRE(cond, ...)                                                          \
+  do {                                                                                  \
+    if (!(cond)) {                                                                      \
+      ::csg::set_error(__VA_ARGS__);                                                    \
+      return false;                                                                     \
+    }                                                                                   \
+  } while (0)
+
+// ---- context ---------------------------------------------------------------
+// Counterpart of sporder::context (sporder/src/common/context.h:67-197): one
+// stream, the device it was created on, and a grow-only device workspace so a
+// warm call allocates nothing.
+struct Context {
+  int device = 0;
+  cudaStream_t stream = nullptr;  // stream every launch of this context uses
+  cudaStream_t own_stream = nullptr;
+  int num_sms = 0;
+  int smem_optin = 0;  // max dynamic shared memory per block (opt-in)
+  char *ws = nullptr;  // device workspace
+  size_t ws_bytes = 0;
+  cudaEvent_t ev[8] = {};
+  int *h_pinned = nullptr;  // small pinned host buffer for counters (64 ints)
+};
+
+bool ensure_workspace(Context &ctx, size_t bytes);
+
+// Bump allocator over the context workspace (256-byte aligned blocks).
+struct Arena {
+  size_t off = 0;
+  size_t take(size_t bytes) {
+    size_t o = off;
+    off += (bytes + 255) & ~size_t(255);
+    return o;
+  }
+};
+
+// ---- resolved csg parameters (sporder/src/sporder.cpp:147-161) ---------------
+struct CsgParams {
+  int32_t k;
+  float ovs;
+  int32_t chunk;
+  int32_t m_used;  // value the stats struct reports
+  int32_t M;       // sketch capacity actually used (multiple of 32, <= 512)
+};
+bool resolve_params(int32_t n, int32_t nnz, int32_t k, float ovs, int32_t chunk, CsgParams *out);
+
+// ---- device scratch of one csg call -------------------------------------------
+struct CsgScratch {
+  // chunk-local transpose (see transpose.cu)
+  uint32_t *keyA, *keyB, *payA, *payB;  // ping-pong buffers of the global sort path
+  int2 *cand;                           // (row, row length) grouped by (chunk, column), rows ascending
+  int2 *seg;                            // per nonzero: (first index into cand, group length)
+  uint32_t *row_work;                   // candidates each row will see
+  // work list of rows with candidates, heaviest bucket first
+  int32_t *row_list;
+  uint32_t *ctrl;  // [0]=chunk ticket [1]=row ticket [2]=rows listed [3..] see CTRL_* below
+  uint64_t *table;  // n*k packed top-k entries
+  uint32_t *gbitmaps;  // greedy bitmaps when they do not fit shared memory, else nullptr
+};
+enum {
+  CTRL_CHUNK_TICKET = 0,
+  CTRL_ROW_TICKET = 1,
+  CTRL_ROWS_LISTED = 2,
+  CTRL_BUCKET_COUNT = 8,   // 33 entries
+  CTRL_BUCKET_BASE = 48,   // 33 entries
+  CTRL_BUCKET_FILL = 88,   // 33 entries
+  CTRL_STATS = 128,        // see stats.cu
+  CTRL_WORDS = 160
+};
+
+// stage launchers; all enqueue on ctx.stream and return false after set_error()
+bool launch_transpose(Context &ctx, int32_t n, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
+                      const int32_t *d_ind, CsgScratch &s);
+bool launch_sketch(Context &ctx, int32_t n, const CsgParams &p, const int32_t *d_ptr,
+                   CsgScratch &s);
+bool launch_greedy(Context &ctx, int32_t n, const CsgParams &p, CsgScratch &s,
+                   int32_t *d_new_order, bool with_stats);
+bool launch_table_stats(Context &ctx, int32_t n, int32_t k, const uint64_t *table, uint32_t *ctrl);
+
+bool launch_reorder(Context &ctx, int32_t n, int32_t nnz, const int32_t *d_ptr_old,
+                    const int32_t *d_ind_old, const float *d_val_old, const int32_t *d_new_order,
+                    int mode, int32_t *d_ptr_new, int32_t *d_ind_new, float *d_val_new);
+size_t reorder_workspace_bytes(int32_t n, int32_t nnz, int mode);
+
+bool launch_spmm(Context &ctx, int32_t n, int32_t nnz, int32_t w, const int32_t *d_ptr,
+                 const int32_t *d_ind, const float *d_val, const float *d_B, float *d_C);
+
+// ---- small device helpers -------------------------------------------------------
+#ifdef __CUDACC__
+constexpr unsigned FULL = 0xFFFFFFFFu;
+__device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
+
+// packed entry of the top-k table; wire format of the reference
+// (sporder/src/common/weighted_index.h:15-27): high word = fp32 bits of the
+// weight, low word = index + 1, all-zero = empty.
+__device__ __forceinline__ uint64_t pack_entry(int32_t idx, float w) {
+  return (static_cast<uint64_t>(__float_as_uint(w)) << 32) | static_cast<uint32_t>(idx + 1);
+}
+__device__ __forceinline__ int32_t entry_index(uint64_t e) {
+  return static_cast<int32_t>(static_cast<uint32_t>(e)) - 1;
+}
+__device__ __forceinline__ uint32_t entry_weight_bits(uint64_t e) {
+  return static_cast<uint32_t>(e >> 32);
+}
+#endif
+
+}  // namespace csg

@@ -1,0 +1,213 @@
+// Greedy chaining inside each chunk, and the optional table statistics.
+//
+// Semantics restated from sporder/src/csg/chunk_similarity_greedy.cu:14-96: the
+// chain starts at the chunk's first row; the next row is the unvisited in-chunk
+// entry of the current row's top-k list with the largest weight (ties: smaller
+// index); with none left the chain restarts at the smallest unvisited row
+// (sporder/src/common/warp_visited_bitmap.cuh:99-111).  The visiting order is the
+// permutation (new2old).
+//
+// One warp per chunk as in the reference; what changes: rows whose candidate
+// stream was empty are known from the transpose (row_work == 0) and need no table
+// load, the restart scan keeps a monotone cursor instead of rescanning the bitmap,
+// the arg-max is two warp reductions, and the order is written 32 entries at a time.
+#include "common.cuh"
+
+namespace csg {
+
+namespace {
+
+constexpr int G_WARPS = 4;
+
+struct GreedyArgs {
+  int32_t n, k, chunk, num_chunks;
+  const uint64_t *table;
+  const uint32_t *row_work;
+  int32_t *order;
+  uint32_t *ctrl;      // stats block, or nullptr
+  uint32_t *gbitmaps;  // global bitmaps when a chunk's bitmaps do not fit shared memory
+  int32_t words;       // bitmap words per chunk
+};
+
+struct ChainStats {  // lives at ctrl[CTRL_STATS ...]
+  unsigned long long total_degree;
+  double total_weight;
+  double link_weight_sum;
+  int32_t zero_degree_rows;
+  int32_t restarts;
+  int32_t links;
+  int32_t pad;
+};
+
+__global__ void __launch_bounds__(G_WARPS * 32) greedy_kernel(GreedyArgs a) {
+  extern __shared__ uint32_t g_smem[];
+  const int lane = lane_id(), warp = threadIdx.x >> 5;
+  const int32_t q = blockIdx.x * G_WARPS + warp;
+  if (q >= a.num_chunks) return;
+  const int64_t start64 = static_cast<int64_t>(q) * a.chunk;
+  const int32_t start = static_cast<int32_t>(start64);
+  const int32_t end = (start64 + a.chunk > a.n) ? a.n : static_cast<int32_t>(start64 + a.chunk);
+  const int32_t size = end - start;
+  const int32_t words = (size + 31) >> 5;
+  // two bitmaps per chunk: visited, and "row has a non-empty top-k list"
+  uint32_t *visited = a.gbitmaps ? a.gbitmaps + static_cast<size_t>(q) * 2 * a.words
+                                 : g_smem + static_cast<size_t>(warp) * 2 * a.words;
+  uint32_t *nonempty = visited + a.words;
+  for (int32_t w = lane; w < words; w += 32) visited[w] = 0;
+  for (int32_t base = 0; base < size; base += 32) {
+    const int32_t i = base + lane;
+    const bool ne = (i < size) && a.row_work[start + i] != 0;
+    const unsigned m = __ballot_sync(FULL, ne);
+    if (lane == 0) nonempty[base >> 5] = m;
+  }
+  __syncwarp();
+
+  int32_t cur = start, emitted = 0, scan = 0, mine = 0;
+  int32_t restarts = 0, links = 0;
+  float link_w = 0.0f;
+  for (;;) {
+    const int32_t loc = cur - start;
+    if (lane == 0) visited[loc >> 5] |= 1u << (loc & 31);
+    if (lane == (emitted & 31)) mine = cur;
+    ++emitted;
+    if ((emitted & 31) == 0) a.order[start + emitted - 32 + lane] = mine;
+    __syncwarp();
+
+    int32_t best_c = -1;
+    if (nonempty[loc >> 5] & (1u << (loc & 31))) {
+      const uint64_t *row = a.table + static_cast<size_t>(cur) * a.k;
+      uint32_t best_w = 0;  // weight bits; real weights are positive
+      for (int32_t j = lane; j < a.k; j += 32) {
+        const uint64_t e = row[j];
+        const int32_t cand = entry_index(e);
+        if (cand < 0) break;  // valid entries form a prefix
+        if (cand < start || cand >= end) continue;
+        const int32_t cl = cand - start;
+        if (visited[cl >> 5] & (1u << (cl & 31))) continue;
+        const uint32_t wb = entry_weight_bits(e);
+        if (wb > best_w || (wb == best_w && cand < best_c)) {
+          best_w = wb;
+          best_c = cand;
+        }
+      }
+      const uint32_t g = __reduce_max_sync(FULL, best_w);
+      if (g != 0u) {
+        const uint32_t c = (best_w == g) ? static_cast<uint32_t>(best_c) : 0xFFFFFFFFu;
+        best_c = static_cast<int32_t>(__reduce_min_sync(FULL, c));
+        links += 1;
+        link_w += __uint_as_float(g);
+      } else {
+        best_c = -1;
+      }
+    }
+    if (best_c >= 0) {
+      cur = best_c;
+      continue;
+    }
+    // restart at the smallest unvisited row; `scan` only moves forward
+    int32_t nxt = -1;
+    for (int32_t base = scan; base < words; base += 32) {
+      const int32_t w = base + lane;
+      uint32_t fr = 0;
+      if (w < words) {
+        fr = ~visited[w];
+        if (w == words - 1 && (size & 31)) fr &= (1u << (size & 31)) - 1u;
+      }
+      const unsigned m = __ballot_sync(FULL, fr != 0);
+      if (m) {
+        const int l = __ffs(m) - 1;
+        const uint32_t f = __shfl_sync(FULL, fr, l);
+        scan = base + l;
+        nxt = (scan << 5) + __ffs(f) - 1;
+        break;
+      }
+    }
+    if (nxt < 0) break;
+    cur = start + nxt;
+    restarts += 1;
+  }
+  if ((emitted & 31) != 0 && lane < (emitted & 31)) a.order[start + (emitted & ~31) + lane] = mine;
+
+  if (a.ctrl && lane == 0) {
+    ChainStats *st = reinterpret_cast<ChainStats *>(a.ctrl + CTRL_STATS);
+    atomicAdd(&st->restarts, restarts);
+    atomicAdd(&st->links, links);
+    atomicAdd(&st->link_weight_sum, static_cast<double>(link_w));
+  }
+}
+
+// sporder/src/common/similarity_top_k.cu:120-157
+__global__ void table_stats_kernel(int32_t n, int32_t k, const uint64_t *__restrict__ table,
+                                   uint32_t *ctrl) {
+  unsigned long long deg = 0;
+  double wsum = 0.0;
+  int32_t zero = 0;
+  for (int32_t r = blockIdx.x * blockDim.x + threadIdx.x; r < n; r += gridDim.x * blockDim.x) {
+    const uint64_t *row = table + static_cast<size_t>(r) * k;
+    int32_t d = 0;
+    float rw = 0.0f;
+    for (int32_t j = 0; j < k; ++j) {
+      const uint64_t e = row[j];
+      if (entry_index(e) == -1) break;
+      d += 1;
+      rw += __uint_as_float(entry_weight_bits(e));
+    }
+    deg += d;
+    wsum += rw;
+    zero += (d == 0);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    deg += __shfl_down_sync(FULL, deg, off);
+    wsum += __shfl_down_sync(FULL, wsum, off);
+    zero += __shfl_down_sync(FULL, zero, off);
+  }
+  if (lane_id() == 0) {
+    ChainStats *st = reinterpret_cast<ChainStats *>(ctrl + CTRL_STATS);
+    if (deg) {
+      atomicAdd(&st->total_degree, deg);
+      atomicAdd(&st->total_weight, wsum);
+    }
+    if (zero) atomicAdd(&st->zero_degree_rows, zero);
+  }
+}
+
+}  // namespace
+
+bool launch_greedy(Context &ctx, int32_t n, const CsgParams &p, CsgScratch &s,
+                   int32_t *d_new_order, bool with_stats) {
+  GreedyArgs a;
+  a.n = n;
+  a.k = p.k;
+  a.chunk = p.chunk;
+  a.num_chunks = static_cast<int32_t>((static_cast<int64_t>(n) + p.chunk - 1) / p.chunk);
+  a.table = s.table;
+  a.row_work = s.row_work;
+  a.order = d_new_order;
+  a.ctrl = with_stats ? s.ctrl : nullptr;
+  const int32_t span = p.chunk < n ? p.chunk : n;
+  a.words = (span + 31) / 32;
+  size_t smem = static_cast<size_t>(G_WARPS) * 2 * a.words * sizeof(uint32_t);
+  a.gbitmaps = nullptr;
+  if (smem > 48 * 1024) {  // very large chunks: bitmaps in global memory
+    CSG_REQUIRE(s.gbitmaps != nullptr, "greedy: no global bitmap space was reserved");
+    a.gbitmaps = s.gbitmaps;
+    smem = 0;
+  }
+  const int grid = (a.num_chunks + G_WARPS - 1) / G_WARPS;
+  greedy_kernel<<<grid, G_WARPS * 32, smem, ctx.stream>>>(a);
+  CSG_CUDA(cudaGetLastError());
+  count_launches(1);
+  return true;
+}
+
+bool launch_table_stats(Context &ctx, int32_t n, int32_t k, const uint64_t *table, uint32_t *ctrl) {
+  int grid = (n + 255) / 256;
+  if (grid > ctx.num_sms * 8) grid = ctx.num_sms * 8;
+  table_stats_kernel<<<grid, 256, 0, ctx.stream>>>(n, k, table, ctrl);
+  CSG_CUDA(cudaGetLastError());
+  count_launches(1);
+  return true;
+}
+
+}  // namespace csg

@@ -1,0 +1,139 @@
+/*
+ * sporder_b200.h -- C ABI of the B200 (sm_100a) Chunked Greedy library.
+ *
+ * The first four entry points are the ones the reference's Python binding and C
+ * callers bind for the csg path; names, argument order, argument meaning and
+ * struct layouts are those of the reference header, so a program linked against
+ * the reference's libsporder can load this library instead for that path.
+ * Everything below them is new surface without a reference counterpart.
+ *
+ * Conventions (same as sporder/include/sporder.h:13-41 unless stated):
+ *   - calls are synchronous: results are ready when the call returns;
+ *   - d_ pointers are device memory on the context's device, h_ pointers are host
+ *     memory, all other pointers are host memory;
+ *   - CSR patterns are square, zero-based, column indices sorted and unique
+ *     inside a row;
+ *   - permutations are new2old: new row p holds old row d_new_order[p];
+ *   - DIFFERENCE: the reference aborts the process on invalid arguments and CUDA
+ *     errors (sporder/src/common/error_checking.h:20-29).  This library never
+ *     aborts: the call returns early, outputs are unspecified, and
+ *     sporder_last_error() returns the message (NULL when the last call on this
+ *     thread succeeded).
+ *   - `is_symmetric` is accepted for compatibility and does not change the
+ *     result: the library always uses the transpose of the pattern, which is what
+ *     the reference reads when the promise is true
+ *     (sporder/src/common/csr2csc.h:49-59).
+ */
+#ifndef SPORDER_B200_H
+#define SPORDER_B200_H
+
+#include <stdbool.h>
+#include <stdint.h>
+
+#define SPORDER_API __attribute__((visibility("default")))
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* replaces sporder/include/sporder.h:43-52 */
+typedef struct sporder_context_struct *sporder_context_t;
+SPORDER_API sporder_context_t sporder_context_create(void);
+SPORDER_API void sporder_context_destroy(sporder_context_t h);
+
+/* replaces sporder/include/sporder.h:203-211 (same layout) */
+typedef struct {
+  double wall_ms;
+  float csr2csc_ms;      /* here: the chunk-local transpose */
+  float similarity_ms;   /* sketch + top-k */
+  float chunk_greedy_ms; /* greedy chaining */
+} sporder_csg_timing_t;
+
+/* replaces sporder/include/sporder.h:213-222 (same layout) */
+typedef struct {
+  int32_t k_used;
+  int32_t m_used;
+  double avg_degree;
+  double avg_edge_weight;
+  int32_t zero_degree_rows;
+  int32_t chunk_size_used;
+  int32_t chain_restarts;
+  double avg_followed_weight;
+} sporder_csg_stats_t;
+
+/* replaces sporder/include/sporder.h:224-228.
+ * k <= 0 -> min(256, max(16, nnz / n)); oversampling <= 0 -> 4.0;
+ * chunk_size <= 0 -> 1024 (sporder/src/sporder.cpp:147-155).
+ * Errors (instead of the reference's abort): oversampling in (0,1),
+ * int(k * oversampling) > 512, n < 1. */
+SPORDER_API void sporder_chunk_similarity_greedy(
+    sporder_context_t ctx, int32_t n, int32_t nnz, const int32_t *d_ptr, const int32_t *d_ind,
+    bool is_symmetric, int32_t k, float oversampling, int32_t chunk_size, int32_t *d_new_order,
+    sporder_csg_timing_t *timing, sporder_csg_stats_t *stats);
+
+/* replaces sporder/include/sporder.h:230-233 */
+typedef enum {
+  SPORDER_REORDER_ROWS = 0,
+  SPORDER_REORDER_SYMMETRIC = 1,
+} sporder_reorder_mode_t;
+
+/* replaces sporder/include/sporder.h:253-258 */
+SPORDER_API void sporder_reorder(sporder_context_t ctx, int32_t n, int32_t nnz,
+                                 const int32_t *d_ptr_old, const int32_t *d_ind_old,
+                                 const float *d_val_old, const int32_t *d_new_order,
+                                 sporder_reorder_mode_t mode, int32_t *d_ptr_new,
+                                 int32_t *d_ind_new, float *d_val_new);
+
+/* ---- new surface (no counterpart in the reference) ------------------------- */
+
+/* Message of the last failed call on this thread, or NULL. */
+SPORDER_API const char *sporder_last_error(void);
+
+/* Run the context's work on `stream` (a cudaStream_t) instead of the context's
+ * private stream; NULL restores the private stream.  Calls stay synchronous. */
+SPORDER_API void sporder_context_set_stream(sporder_context_t ctx, void *stream);
+
+/* Bytes of device workspace the context currently holds (grow-only cache). */
+SPORDER_API uint64_t sporder_context_workspace_bytes(sporder_context_t ctx);
+
+/* csg that also returns the top-k table: d_table receives n * k_used packed
+ * entries (high 32 bits = fp32 bits of the weight, low 32 bits = index + 1,
+ * 0 = empty; the reference's internal format, sporder/src/common/weighted_index.h:15-27).
+ * d_table_capacity is the number of entries d_table can hold; d_new_order may be
+ * NULL to skip the greedy stage.  Returns k_used, or -1 on error. */
+SPORDER_API int32_t sporder_csg_with_table(sporder_context_t ctx, int32_t n, int32_t nnz,
+                                           const int32_t *d_ptr, const int32_t *d_ind,
+                                           bool is_symmetric, int32_t k, float oversampling,
+                                           int32_t chunk_size, int32_t *d_new_order,
+                                           uint64_t *d_table, uint64_t d_table_capacity,
+                                           sporder_csg_timing_t *timing,
+                                           sporder_csg_stats_t *stats);
+
+/* csg on host buffers: copies ptr/ind to the device, reorders, copies the
+ * permutation back.  Returns 0, or -1 on error. */
+SPORDER_API int32_t sporder_chunk_similarity_greedy_host(
+    sporder_context_t ctx, int32_t n, int32_t nnz, const int32_t *h_ptr, const int32_t *h_ind,
+    bool is_symmetric, int32_t k, float oversampling, int32_t chunk_size, int32_t *h_new_order,
+    sporder_csg_timing_t *timing, sporder_csg_stats_t *stats);
+
+/* fp32 CSR SpMM: C[n x w] = A * B with B, C row-major (ld = w).  The reference
+ * times third-party kernels (bench/spmm/spmm_bench/base.py:48-59) and cuSPARSE
+ * (sporder/src/bench_cusparse_spmm.cu:64-90) here; it has no SpMM of its own.
+ * Returns 0, or -1 on error. */
+SPORDER_API int32_t sporder_spmm(sporder_context_t ctx, int32_t n, int32_t nnz, int32_t w,
+                                 const int32_t *d_ptr, const int32_t *d_ind, const float *d_val,
+                                 const float *d_B, float *d_C);
+
+/* Same without the final stream synchronisation (for callers that time a train
+ * of launches with events on the context's stream).  Returns 0 or -1. */
+SPORDER_API int32_t sporder_spmm_async(sporder_context_t ctx, int32_t n, int32_t nnz, int32_t w,
+                                       const int32_t *d_ptr, const int32_t *d_ind,
+                                       const float *d_val, const float *d_B, float *d_C);
+
+/* Number of kernels this library has launched in this process (all contexts). */
+SPORDER_API uint64_t sporder_kernel_launches(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPORDER_B200_H */
