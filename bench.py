@@ -1,0 +1,439 @@
+#!/usr/bin/env python
+"""Benchmark of the csg reorder path (and the SpMM it feeds) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+A step is one csg reorder of the workload matrix: chunk-local transpose, sketch +
+top-k, greedy.  The workload is the power-law matrix the headline target is quoted
+on: R-MAT scale 22, edge factor 16, (a,b,c,d) = (.57,.19,.19,.05), duplicates
+removed, seed 3 (seeded synthetic data standing in for the reference's SuiteSparse
+sets), csg with the reference's default parameters (k = nnz/n clamped to [16,256],
+oversampling 4, chunk 1024).
+
+Prints ONE JSON line.  `value` is Mnnz/s with the matrix resident in HBM, timed with
+CUDA events on the launching stream; `e2e` is the same metric through the host-buffer
+entry point of the C ABI (pinned host CSR in, permutation out, copies inside the timed
+region).  With N > 1 (launched under torchrun) the rows are cut into N chunk-aligned
+shards, one per GPU, and the permutation shards are all-gathered with NCCL; the total
+work is fixed, so scaling is "strong".
+
+`--impl reference` times the CPU restatement of the reference's algorithm (the
+reference has no CPU implementation of csg; its own code is CUDA) on the host cores,
+each step on a bounded sample of whole chunks of the same matrix.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = "rmat22"
+CSG_KW = dict(k=0, oversampling=0.0, chunk_size=0)  # configs/paper.yaml:6 -> all "auto"
+CHUNK = 1024
+
+
+# ---------------------------------------------------------------------------------
+T_START = time.time()
+
+
+def log(*a):
+    print("[bench %7.1fs]" % (time.time() - T_START), *a, file=sys.stderr, flush=True)
+
+
+def load_workload(scale):
+    """The R-MAT matrix (host numpy int32 CSR), cached in /tmp between runs."""
+    from chunkedgreedy_b200 import synth
+    cache = "/tmp/chunkedgreedy_b200_rmat%d_seed3.npz" % scale
+    if os.path.exists(cache):
+        try:
+            z = np.load(cache)
+            return z["ptr"], z["ind"], z["val"]
+        except Exception:
+            pass
+    ptr, ind, val = synth.rmat(scale=scale, edge_factor=16, seed=3)
+    try:
+        tmp = cache + ".%d.tmp.npz" % os.getpid()
+        np.savez(tmp, ptr=ptr, ind=ind, val=val)
+        os.replace(tmp, cache)
+    except Exception:
+        pass
+    return ptr, ind, val
+
+
+def chunk_sample(ptr, ind, fraction, chunk=CHUNK):
+    """A bounded sample of the workload made of whole chunks: chunks are sorted by their
+    nonzero count and every (1/fraction)-th is taken, so light and heavy chunks appear in
+    proportion.  Returns a CSR block (rows renumbered, columns kept) and its nnz."""
+    n = ptr.size - 1
+    nch = (n + chunk - 1) // chunk
+    if fraction >= 1.0:
+        return ptr, ind, nch
+    edges = np.minimum(np.arange(nch + 1, dtype=np.int64) * chunk, n)
+    cnt = np.diff(ptr[edges].astype(np.int64))
+    order = np.argsort(-cnt, kind="stable")
+    stride = max(1, int(round(1.0 / fraction)))
+    take = np.sort(order[stride // 2::stride])
+    take = take[take != nch - 1] if (n % chunk) else take  # keep full-size chunks only
+    pieces_ptr, pieces_ind, base = [np.zeros(1, dtype=np.int64)], [], 0
+    for q in take:
+        r0, r1 = int(edges[q]), int(edges[q + 1])
+        b, e = int(ptr[r0]), int(ptr[r1])
+        pieces_ptr.append(ptr[r0 + 1:r1 + 1].astype(np.int64) - b + base)
+        pieces_ind.append(ind[b:e])
+        base += e - b
+    return (np.concatenate(pieces_ptr).astype(np.int32),
+            np.concatenate(pieces_ind) if pieces_ind else np.zeros(0, np.int32), len(take))
+
+
+def cpu_reference_rate(ptr, ind, k, budget_s, steps_total, threads=None):
+    """Times the CPU restatement (oracle/) on a sample sized so that `steps_total` steps
+    fit in about `budget_s` seconds.  Returns (callable running one step -> seconds,
+    sample nnz, description)."""
+    import oracle
+    if threads:
+        oracle.set_num_threads(threads)
+    n = ptr.size - 1
+    # probe on 1/64 of the chunks to size the real sample
+    pp, pi, pc = chunk_sample(ptr, ind, 1.0 / 64)
+    t0 = time.perf_counter()
+    oracle.csg(pp, pi, False, k=k, ncols=n)
+    probe = time.perf_counter() - t0
+    rate = max(pi.size, 1) / max(probe, 1e-6)  # nnz / s
+    want = rate * budget_s / max(steps_total, 1)
+    fraction = min(1.0, max(1.0 / 64, want / max(ind.size, 1)))
+    sp_, si_, sc = chunk_sample(ptr, ind, fraction)
+
+    def step():
+        t = time.perf_counter()
+        oracle.csg(sp_, si_, False, k=k, ncols=n)
+        return time.perf_counter() - t
+
+    nch = (n + CHUNK - 1) // CHUNK
+    desc = "%d of %d chunks (every %d-th by nonzero count), %d nnz, full csg per step" % (
+        sc, nch, max(1, int(round(1.0 / fraction))), si_.size)
+    return step, int(si_.size), desc
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.lines, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)),
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------
+def run_reference(args, rank, world):
+    """CPU arm: rank 0 alone works; the other ranks exit 0."""
+    if rank != 0:
+        return
+    import oracle
+    ptr, ind, _ = load_workload(args.scale)
+    n, nnz = ptr.size - 1, ind.size
+    k = min(256, max(16, nnz // n))
+    step, sample_nnz, desc = cpu_reference_rate(ptr, ind, k, args.cpu_budget,
+                                                args.steps + args.warmup)
+    for _ in range(args.warmup):
+        step()
+    total = sum(step() for _ in range(args.steps))
+    value = sample_nnz * args.steps / total / 1e6
+    cores = oracle.num_threads()
+    line = {
+        "impl": "reference", "metric": "csg reorder throughput", "value": value, "unit": "Mnnz/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int32 indices, f32 weights", "data": "synthetic",
+        "config": workload_config(n, nnz, k, args),
+        "cpu_baseline": {"value": value, "unit": "Mnnz/s", "cores": cores, "kind": "port",
+                         "sample": desc},
+        "e2e": {"value": value, "unit": "Mnnz/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "note": "the reference implements csg only in CUDA; this arm is the OpenMP restatement "
+                "of its arithmetic (oracle/csg_oracle.c) on the host cores",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n, nnz, k, args):
+    return {"workload": "rmat scale %d ef16 a.57 b.19 c.19 d.05 dedup seed3; csg k=%d M=%d chunk=%d"
+                        % (args.scale, k, ((4 * k + 31) // 32) * 32, CHUNK),
+            "n": int(n), "nnz": int(nnz), "parallelism": "row shards x%d" % args.gpus,
+            "l2": "inputs and scratch (>1 GB) exceed L2; no explicit flush"}
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    import chunkedgreedy_b200 as sp
+    from chunkedgreedy_b200 import dist as csgdist
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    ptr, ind, val = load_workload(args.scale)
+    n, nnz = ptr.size - 1, ind.size
+    k = csgdist.resolve_k(n, nnz, 0)
+    bounds = csgdist.shard_bounds(ptr, CHUNK, world)
+    r0, r1 = bounds[rank]
+    pl, il = csgdist.extract_shard(ptr, ind, r0, r1)
+    h_ptr = torch.from_numpy(np.ascontiguousarray(pl)).pin_memory()
+    h_ind = torch.from_numpy(np.ascontiguousarray(il)).pin_memory()
+    d_ptr, d_ind = h_ptr.to(dev), h_ind.to(dev)
+    ctx = sp.Context()
+    log("rank", rank, "rows", r0, r1, "nnz", il.size, "k", k)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step_device():
+        local = csgdist.csg_shard(d_ptr, d_ind, n, r0, k=k, chunk_size=CHUNK, ctx=ctx)
+        return csgdist.gather_shards(local, bounds) if world > 1 else local
+
+    h_out = torch.empty(n, dtype=torch.int32).pin_memory()
+
+    def step_e2e():
+        dp = h_ptr.to(dev, non_blocking=True)
+        di = h_ind.to(dev, non_blocking=True)
+        local = csgdist.csg_shard(dp, di, n, r0, k=k, chunk_size=CHUNK, ctx=ctx)
+        full = csgdist.gather_shards(local, bounds) if world > 1 else local
+        h_out.copy_(full, non_blocking=True)
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing --------------------------------------------------
+    for _ in range(args.warmup):
+        order = step_device()
+        log("warm-up step done")
+    barrier()
+    launches0 = sp.kernel_launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            order = step_device()
+        e1.record()
+        barrier()
+    launches = sp.kernel_launches() - launches0
+    t_ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+    t_ms = float(t_ms.item())
+    value = nnz * args.steps / (t_ms * 1e-3) / 1e6
+
+    log("timed: %.2f ms/step" % (t_ms / args.steps))
+    # ---- stage times (CUDA events recorded by the library on the same stream) ------
+    stage = {"transpose_ms": 0.0, "sketch_ms": 0.0, "greedy_ms": 0.0}
+    reps = max(1, min(args.steps, 5))
+    for _ in range(reps):
+        _, tm = csgdist.csg_shard(d_ptr, d_ind, n, r0, k=k, chunk_size=CHUNK, ctx=ctx,
+                                  with_timing=True)
+        stage["transpose_ms"] += tm["csr2csc_ms"] / reps
+        stage["sketch_ms"] += tm["similarity_ms"] / reps
+        stage["greedy_ms"] += tm["chunk_greedy_ms"] / reps
+    n_loc, nnz_loc = r1 - r0, il.size
+
+    log("stages", stage)
+    # ---- end to end through the host-buffer path -------------------------------------
+    for _ in range(min(args.warmup, 2)):
+        step_e2e()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step_e2e()
+    barrier()
+    e2e_s = torch.tensor([time.perf_counter() - t0], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    e2e_value = nnz * args.steps / float(e2e_s.item()) / 1e6
+
+    log("e2e done")
+    if rank != 0:
+        return
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+    # algorithmic bytes of the sketch/top-k stage of THIS rank's shard: the pattern read
+    # once row-wise and once in transposed view, the table written once
+    b_sketch = 2 * (4 * (n_loc + 1) + 4 * nnz_loc) + 8 * n_loc * k
+    ach = b_sketch / (stage["sketch_ms"] * 1e-3) / 1e9 if stage["sketch_ms"] > 0 else 0.0
+    line = {
+        "metric": "csg reorder throughput", "value": value, "unit": "Mnnz/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_ms / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int32 indices, f32 weights", "data": "synthetic",
+        "config": workload_config(n, nnz, k, args),
+        "e2e": {"value": e2e_value, "unit": "Mnnz/s",
+                "h2d_bytes_per_step": int(4 * (n_loc + 1) + 4 * nnz_loc),
+                "d2h_bytes_per_step": int(4 * n)},
+        "gpu_launches": int(launches),
+        "clocks": clocks.summary(),
+        "stages_ms": stage,
+        "roofline": {"bound": "hbm", "kernel": "sketch_kernel (sketch + top-k)", "achieved": ach,
+                     "peak": hbm, "unit": "GB/s", "frac": ach / hbm, "peak_source": peak_src,
+                     "algorithmic_bytes": int(b_sketch),
+                     "traffic": TRAFFIC_FROM_NCU.get("sketch_kernel")},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        import oracle
+        step, sample_nnz, desc = cpu_reference_rate(ptr, ind, k, args.cpu_budget, 1)
+        secs = step()
+        line["cpu_baseline"] = {"value": sample_nnz / secs / 1e6, "unit": "Mnnz/s",
+                                "cores": oracle.num_threads(), "kind": "port", "sample": desc}
+        log("cpu baseline done")
+    if world == 1 and not args.no_ref_cuda:
+        line["reference_cuda"] = reference_cuda(d_ptr, d_ind, nnz)
+        log("reference cuda done", line["reference_cuda"])
+    if world == 1 and not args.no_spmm:
+        line["spmm"] = spmm_section(sp, ctx, d_ptr, d_ind, torch.from_numpy(val).to(dev), order,
+                                    n, nnz, hbm)
+    print(json.dumps(line), flush=True)
+
+
+# per-launch DRAM traffic of the dominant kernel from an ncu capture (see profiles/)
+TRAFFIC_FROM_NCU = {}
+
+
+def reference_cuda(d_ptr, d_ind, nnz):
+    """The reference's own CUDA library, built unchanged for sm_100a (oracle/_ref), on the
+    same matrix with its benchmark protocol (one warm-up call, then the library's wall_ms;
+    bench/reorder/reorder_bench/methods/sporder_csg.py:41-57)."""
+    try:
+        from oracle import ref
+        if not ref.available():
+            return {"unavailable": "oracle/_ref/libsporder_ref.so not present"}
+        import torch
+        ref.csg(d_ptr, d_ind, False)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=d_ptr.device)
+        flush.zero_()
+        _, tm = ref.csg(d_ptr, d_ind, False, with_timing=True)
+        return {"value": nnz / (tm["wall_ms"] * 1e-3) / 1e6, "unit": "Mnnz/s", "timing_ms": tm,
+                "kind": "reference CUDA sources compiled for sm_100a, 1 GPU"}
+    except Exception as e:  # never let the comparison leg break the bench line
+        return {"unavailable": repr(e)[:200]}
+
+
+def spmm_section(sp, ctx, d_ptr, d_ind, d_val, order, n, nnz, hbm, widths=(32, 128)):
+    """Post-reorder SpMM: GFLOP/s = 2*nnz*w / t (spmatkit/spmatkit.py:2150-2155) on
+    A' = P A P^T and on A, with the library's fp32 kernel."""
+    import torch
+    out = {}
+    p2, i2, v2 = sp.reorder(d_ptr, d_ind, order, val=d_val, symmetric=True, ctx=ctx)
+    for w in widths:
+        B = torch.randn((n, w), device=d_ptr.device, dtype=torch.float32)
+        C = torch.empty_like(B)
+        res = {}
+        for tag, (pp, ii, vv) in (("original", (d_ptr, d_ind, d_val)), ("reordered", (p2, i2, v2))):
+            for _ in range(3):
+                sp.spmm(pp, ii, vv, B, out=C, ctx=ctx, sync=False)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 10
+            e0.record()
+            for _ in range(reps):
+                sp.spmm(pp, ii, vv, B, out=C, ctx=ctx, sync=False)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / reps
+            algo = 4 * (n + 1) + 8 * nnz + 8 * n * w  # pattern + values once, B and C once
+            res[tag] = {"ms": ms, "gflops": 2.0 * nnz * w / (ms * 1e6),
+                        "roofline_frac": algo / (ms * 1e-3) / 1e9 / hbm}
+        res["speedup"] = res["original"]["ms"] / res["reordered"]["ms"]
+        out["w%d" % w] = res
+        del B, C
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--scale", type=int, default=22, help="R-MAT scale (22 = the named workload)")
+    ap.add_argument("--cpu-budget", type=float, default=20.0,
+                    help="seconds of CPU work the baseline sample is sized for")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-ref-cuda", action="store_true")
+    ap.add_argument("--no-spmm", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        args.cpu_budget = max(args.cpu_budget, 60.0)
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -93,8 +93,9 @@ def _enter(ctx, ref):
     """Bind the context to the caller's current stream so that work queued by the
     caller before the call is ordered before ours."""
     torch = _torch()
-    stream = torch.cuda.current_stream(ref.device)
-    _lib.load().sporder_context_set_stream(ctx.handle, C.c_void_p(stream.cuda_stream))
+    stream = torch.cuda.current_stream(ref.device).cuda_stream
+    # handle 0 is the legacy default stream; the C ABI wants its explicit name (0x1)
+    _lib.load().sporder_context_set_stream(ctx.handle, C.c_void_p(stream if stream else 1))
 
 
 def _sizes(ptr, ind):

@@ -41,6 +41,9 @@ SYMBOLS = {
     "sporder_csg_with_table": (C.c_int32, [_P, C.c_int32, C.c_int32, _P, _P, C.c_bool, C.c_int32,
                                            C.c_float, C.c_int32, _P, _P, C.c_uint64,
                                            C.POINTER(CsgTiming), C.POINTER(CsgStats)]),
+    "sporder_csg_shard": (C.c_int32, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P,
+                                      C.c_int32, C.c_float, C.c_int32, _P, _P, C.c_uint64,
+                                      C.POINTER(CsgTiming), C.POINTER(CsgStats)]),
     "sporder_chunk_similarity_greedy_host": (C.c_int32, [_P, C.c_int32, C.c_int32, _P, _P,
                                                          C.c_bool, C.c_int32, C.c_float, C.c_int32,
                                                          _P, C.POINTER(CsgTiming),

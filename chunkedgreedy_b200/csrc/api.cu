@@ -127,7 +127,8 @@ bool plan_scratch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, uint
 
 // The pipeline of sporder/src/csg/chunk_similarity_greedy.cu:100-138 with the
 // stages of this library: chunk-local transpose -> sketch/top-k -> greedy.
-bool run_csg(Context &ctx, int32_t n, int32_t nnz, const int32_t *d_ptr, const int32_t *d_ind,
+bool run_csg(Context &ctx, int32_t n, int32_t ncols, int32_t row_base, int32_t nnz,
+             const int32_t *d_ptr, const int32_t *d_ind,
              int32_t k, float ovs, int32_t chunk, int32_t *d_new_order, uint64_t *d_table,
              uint64_t table_capacity, sporder_csg_timing_t *timing, sporder_csg_stats_t *stats,
              int32_t *k_used) {
@@ -142,6 +143,8 @@ bool run_csg(Context &ctx, int32_t n, int32_t nnz, const int32_t *d_ptr, const i
     stats->chunk_size_used = p.chunk;
   }
   CSG_REQUIRE(d_ptr && (d_ind || nnz == 0), "null CSR arrays");
+  CSG_REQUIRE(ncols >= n && row_base >= 0 && static_cast<int64_t>(row_base) + n <= 0x7FFFFFFF,
+              "row block [%d, %d + %d) does not fit %d columns", row_base, row_base, n, ncols);
   CSG_REQUIRE(!d_table || table_capacity >= static_cast<uint64_t>(n) * p.k,
               "table buffer holds %llu entries, need n * k = %llu",
               static_cast<unsigned long long>(table_capacity),
@@ -152,21 +155,25 @@ bool run_csg(Context &ctx, int32_t n, int32_t nnz, const int32_t *d_ptr, const i
   cudaStream_t st = ctx.stream;
 
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[0], st));
-  if (!launch_transpose(ctx, n, nnz, p.chunk, d_ptr, d_ind, s)) return false;
+  if (!launch_transpose(ctx, n, ncols, nnz, p.chunk, d_ptr, d_ind, s)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
-  if (!launch_sketch(ctx, n, p, d_ptr, s)) return false;
+  if (!launch_sketch(ctx, n, nnz, p, d_ptr, s, row_base)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[2], st));
   if (stats && !launch_table_stats(ctx, n, p.k, s.table, s.ctrl)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[3], st));
   if (d_new_order) {
-    if (!launch_greedy(ctx, n, p, s, d_new_order, stats != nullptr)) return false;
+    if (!launch_greedy(ctx, n, p, s, d_new_order, stats != nullptr, row_base)) return false;
   }
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[4], st));
   ChainStatsHost hs;
   if (stats)
     CSG_CUDA(cudaMemcpyAsync(&hs, s.ctrl + CTRL_STATS, sizeof(hs), cudaMemcpyDeviceToHost, st));
+  CSG_CUDA(cudaMemcpyAsync(ctx.h_pinned, s.ctrl + CTRL_BAD_INPUT, sizeof(uint32_t),
+                           cudaMemcpyDeviceToHost, st));
   CSG_CUDA(cudaStreamSynchronize(st));
   CSG_CUDA(cudaGetLastError());
+  CSG_REQUIRE(ctx.h_pinned[0] == 0,
+              "malformed CSR: row pointers must be non-decreasing inside [0, nnz] (results unspecified)");
   if (stats) {  // sporder/src/csg/stats_collector.cu:53-62
     stats->avg_degree = static_cast<double>(hs.total_degree) / n;
     stats->avg_edge_weight =
@@ -232,7 +239,7 @@ void sporder_context_destroy(sporder_context_t h) {
 
 void sporder_context_set_stream(sporder_context_t h, void *stream) {
   if (!h) return;
-  h->c.stream = stream ? static_cast<cudaStream_t>(stream) : h->c.own_stream;
+  h->c.stream = stream ? static_cast<cudaStream_t>(stream) : h->c.own_stream;  // see header
 }
 
 uint64_t sporder_context_workspace_bytes(sporder_context_t h) { return h ? h->c.ws_bytes : 0; }
@@ -256,7 +263,7 @@ void sporder_chunk_similarity_greedy(sporder_context_t ctx, int32_t n, int32_t n
     csg::set_error("null d_new_order");
     return;
   }
-  csg::run_csg(ctx->c, n, nnz, d_ptr, d_ind, k, oversampling, chunk_size, d_new_order, nullptr, 0,
+  csg::run_csg(ctx->c, n, n, 0, nnz, d_ptr, d_ind, k, oversampling, chunk_size, d_new_order, nullptr, 0,
                timing, stats, nullptr);
 }
 
@@ -272,8 +279,25 @@ int32_t sporder_csg_with_table(sporder_context_t ctx, int32_t n, int32_t nnz, co
     return -1;
   }
   int32_t k_used = -1;
-  if (!csg::run_csg(ctx->c, n, nnz, d_ptr, d_ind, k, oversampling, chunk_size, d_new_order, d_table,
+  if (!csg::run_csg(ctx->c, n, n, 0, nnz, d_ptr, d_ind, k, oversampling, chunk_size, d_new_order, d_table,
                     d_table_capacity, timing, stats, &k_used))
+    return -1;
+  return k_used;
+}
+
+int32_t sporder_csg_shard(sporder_context_t ctx, int32_t n_rows, int32_t n_cols, int32_t row_base,
+                          int32_t nnz, const int32_t *d_ptr, const int32_t *d_ind, int32_t k,
+                          float oversampling, int32_t chunk_size, int32_t *d_new_order,
+                          uint64_t *d_table, uint64_t d_table_capacity,
+                          sporder_csg_timing_t *timing, sporder_csg_stats_t *stats) {
+  csg::clear_error();
+  if (!ctx) {
+    csg::set_error("null context");
+    return -1;
+  }
+  int32_t k_used = -1;
+  if (!csg::run_csg(ctx->c, n_rows, n_cols, row_base, nnz, d_ptr, d_ind, k, oversampling,
+                    chunk_size, d_new_order, d_table, d_table_capacity, timing, stats, &k_used))
     return -1;
   return k_used;
 }
@@ -303,7 +327,7 @@ int32_t sporder_chunk_similarity_greedy_host(sporder_context_t ctx, int32_t n, i
     if (nnz > 0)
       CSG_CUDA(cudaMemcpyAsync(d_ind, h_ind, sizeof(int32_t) * static_cast<size_t>(nnz),
                                cudaMemcpyHostToDevice, c.stream));
-    const bool ok = csg::run_csg(c, n, nnz, d_ptr, d_ind, k, oversampling, chunk_size, d_order,
+    const bool ok = csg::run_csg(c, n, n, 0, nnz, d_ptr, d_ind, k, oversampling, chunk_size, d_order,
                                  nullptr, 0, timing, stats, nullptr);
     if (ok)
       CSG_CUDA(cudaMemcpyAsync(h_new_order, d_order, sizeof(int32_t) * static_cast<size_t>(n),

@@ -90,6 +90,7 @@ enum {
   CTRL_CHUNK_TICKET = 0,
   CTRL_ROW_TICKET = 1,
   CTRL_ROWS_LISTED = 2,
+  CTRL_BAD_INPUT = 3,      // set by a kernel that met row pointers outside [0, nnz]
   CTRL_BUCKET_COUNT = 8,   // 33 entries
   CTRL_BUCKET_BASE = 48,   // 33 entries
   CTRL_BUCKET_FILL = 88,   // 33 entries
@@ -98,12 +99,12 @@ enum {
 };
 
 // stage launchers; all enqueue on ctx.stream and return false after set_error()
-bool launch_transpose(Context &ctx, int32_t n, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
+bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
                       const int32_t *d_ind, CsgScratch &s);
-bool launch_sketch(Context &ctx, int32_t n, const CsgParams &p, const int32_t *d_ptr,
-                   CsgScratch &s);
+bool launch_sketch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, const int32_t *d_ptr,
+                   CsgScratch &s, int32_t row_base);
 bool launch_greedy(Context &ctx, int32_t n, const CsgParams &p, CsgScratch &s,
-                   int32_t *d_new_order, bool with_stats);
+                   int32_t *d_new_order, bool with_stats, int32_t row_base);
 bool launch_table_stats(Context &ctx, int32_t n, int32_t k, const uint64_t *table, uint32_t *ctrl);
 
 bool launch_reorder(Context &ctx, int32_t n, int32_t nnz, const int32_t *d_ptr_old,

@@ -20,7 +20,7 @@ namespace {
 constexpr int G_WARPS = 4;
 
 struct GreedyArgs {
-  int32_t n, k, chunk, num_chunks;
+  int32_t n, k, chunk, num_chunks, row_base;
   const uint64_t *table;
   const uint32_t *row_work;
   int32_t *order;
@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(G_WARPS * 32) greedy_kernel(GreedyArgs a) {
   for (;;) {
     const int32_t loc = cur - start;
     if (lane == 0) visited[loc >> 5] |= 1u << (loc & 31);
-    if (lane == (emitted & 31)) mine = cur;
+    if (lane == (emitted & 31)) mine = cur + a.row_base;
     ++emitted;
     if ((emitted & 31) == 0) a.order[start + emitted - 32 + lane] = mine;
     __syncwarp();
@@ -79,8 +79,8 @@ __global__ void __launch_bounds__(G_WARPS * 32) greedy_kernel(GreedyArgs a) {
       uint32_t best_w = 0;  // weight bits; real weights are positive
       for (int32_t j = lane; j < a.k; j += 32) {
         const uint64_t e = row[j];
-        const int32_t cand = entry_index(e);
-        if (cand < 0) break;  // valid entries form a prefix
+        if (e == 0) break;  // valid entries form a prefix
+        const int32_t cand = entry_index(e) - a.row_base;
         if (cand < start || cand >= end) continue;
         const int32_t cl = cand - start;
         if (visited[cl >> 5] & (1u << (cl & 31))) continue;
@@ -175,11 +175,12 @@ __global__ void table_stats_kernel(int32_t n, int32_t k, const uint64_t *__restr
 }  // namespace
 
 bool launch_greedy(Context &ctx, int32_t n, const CsgParams &p, CsgScratch &s,
-                   int32_t *d_new_order, bool with_stats) {
+                   int32_t *d_new_order, bool with_stats, int32_t row_base) {
   GreedyArgs a;
   a.n = n;
   a.k = p.k;
   a.chunk = p.chunk;
+  a.row_base = row_base;
   a.num_chunks = static_cast<int32_t>((static_cast<int64_t>(n) + p.chunk - 1) / p.chunk);
   a.table = s.table;
   a.row_work = s.row_work;

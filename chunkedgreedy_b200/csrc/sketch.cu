@@ -26,7 +26,7 @@ namespace {
 constexpr int S_THREADS = 128;
 
 struct SketchArgs {
-  int32_t n, k;
+  int32_t n, nnz, k, row_base;
   const int32_t *ptr;
   const int2 *seg;
   const int2 *cand;
@@ -141,7 +141,7 @@ struct Sketch {
   }
 
   // writes the valid prefix of the row's k entries (the table is pre-zeroed)
-  __device__ __forceinline__ void select_top_k(int32_t k, uint64_t *out) {
+  __device__ __forceinline__ void select_top_k(int32_t k, uint64_t *out, int32_t row_base) {
     local_sort_descending();
     const int lane = lane_id();
     int pos = 0;
@@ -162,7 +162,7 @@ struct Sketch {
       if (g == 0u) break;  // every lane is past its last filled slot
       const int wl = __ffs(__ballot_sync(FULL, wb == g)) - 1;
       const int32_t ek = __shfl_sync(FULL, kc, wl);
-      if (lane == (i & 31)) mine = pack_entry(ek, __uint_as_float(g));
+      if (lane == (i & 31)) mine = pack_entry(ek + row_base, __uint_as_float(g));
       if (lane == wl) ++pos;
       if ((i & 31) == 31) {
         out[(i - 31) + lane] = mine;
@@ -186,6 +186,10 @@ __global__ void __launch_bounds__(S_THREADS) sketch_kernel(SketchArgs a) {
     const int32_t r = a.row_list[item];
     const int32_t rb = a.ptr[r], re = a.ptr[r + 1];
     const int32_t rs = re - rb;
+    if (rb < 0 || rs < 0 || re > a.nnz) {  // malformed row pointers: flag and skip
+      if (lane == 0) atomicExch(&a.ctrl[CTRL_BAD_INPUT], 1u);
+      continue;
+    }
     sk.clear();
     for (int32_t pb = rb; pb < re; pb += 32) {
       const int32_t p = pb + lane;
@@ -217,7 +221,7 @@ __global__ void __launch_bounds__(S_THREADS) sketch_kernel(SketchArgs a) {
         }
       }
     }
-    sk.select_top_k(a.k, a.table + static_cast<size_t>(r) * a.k);
+    sk.select_top_k(a.k, a.table + static_cast<size_t>(r) * a.k, a.row_base);
   }
 }
 
@@ -234,11 +238,13 @@ bool launch_one(Context &ctx, const SketchArgs &a) {
 
 }  // namespace
 
-bool launch_sketch(Context &ctx, int32_t n, const CsgParams &p, const int32_t *d_ptr,
-                   CsgScratch &s) {
+bool launch_sketch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, const int32_t *d_ptr,
+                   CsgScratch &s, int32_t row_base) {
   SketchArgs a;
   a.n = n;
+  a.nnz = nnz;
   a.k = p.k;
+  a.row_base = row_base;
   a.ptr = d_ptr;
   a.seg = s.seg;
   a.cand = s.cand;

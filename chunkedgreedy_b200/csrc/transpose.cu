@@ -29,7 +29,7 @@ constexpr int T_LS = 15360;                // largest chunk (nonzeros) sorted in
 constexpr int T_RP = 2048;                 // largest chunk (rows) with row tables in shared memory
 
 struct TransposeArgs {
-  int32_t n, chunk, num_chunks, passes;
+  int32_t n, nnz, chunk, num_chunks, passes;
   const int32_t *ptr, *ind;
   uint32_t *keyA, *keyB, *payA, *payB;
   int2 *cand, *seg;
@@ -242,7 +242,11 @@ __global__ void __launch_bounds__(T_THREADS, 1) transpose_kernel(TransposeArgs a
     const int32_t ce = (cs64 + a.chunk > a.n) ? a.n : static_cast<int32_t>(cs64 + a.chunk);
     const int32_t rows = ce - cs;
     const int32_t b = a.ptr[cs];
-    const int L = a.ptr[ce] - b;
+    int L = a.ptr[ce] - b;
+    if (b < 0 || L < 0 || L > a.nnz - b) {  // malformed row pointers: flag and skip
+      if (tid == 0) atomicExch(&a.ctrl[CTRL_BAD_INPUT], 1u);
+      L = 0;
+    }
     const bool rows_in_smem = rows <= T_RP;
     if (rows_in_smem) {
       for (int i = tid; i <= rows; i += T_THREADS) sh.sptr[i] = a.ptr[cs + i];
@@ -324,15 +328,15 @@ __global__ void row_list_kernel(int32_t n, const uint32_t *__restrict__ row_work
 
 }  // namespace
 
-bool launch_transpose(Context &ctx, int32_t n, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
+bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
                       const int32_t *d_ind, CsgScratch &s) {
-  (void)nnz;
   TransposeArgs a;
   a.n = n;
+  a.nnz = nnz;
   a.chunk = chunk;
   a.num_chunks = static_cast<int32_t>((static_cast<int64_t>(n) + chunk - 1) / chunk);
   int bits = 1;
-  while (bits < 32 && (static_cast<int64_t>(1) << bits) < n) ++bits;
+  while (bits < 32 && (static_cast<int64_t>(1) << bits) < ncols) ++bits;  // column ids < ncols
   a.passes = (bits + 7) / 8;
   a.ptr = d_ptr;
   a.ind = d_ind;

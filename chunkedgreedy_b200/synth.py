@@ -30,11 +30,15 @@ __all__ = [
 
 def coo_to_csr(n, rows, cols, vals=None):
     """Sorted, duplicate-free CSR from COO (first value of a duplicate wins)."""
-    rows = np.asarray(rows, dtype=np.int64)
-    cols = np.asarray(cols, dtype=np.int64)
-    key = rows * np.int64(n) + cols
+    key = np.asarray(rows).astype(np.int64)
+    key *= np.int64(n)
+    key += np.asarray(cols)
     if vals is None:
-        key = np.unique(key)
+        key.sort()
+        keep = np.empty(key.size, dtype=bool)
+        keep[:1] = True
+        np.not_equal(key[1:], key[:-1], out=keep[1:])
+        key = key[keep]
         v = None
     else:
         key, first = np.unique(key, return_index=True)
@@ -136,14 +140,18 @@ def road_lattice(n=2_000_000, seed=2, relabel=True):
 def _rmat_edges(scale, edge_factor, probs, rng):
     a, b, c, _ = probs
     m = edge_factor << scale
-    rows = np.zeros(m, dtype=np.int64)
-    cols = np.zeros(m, dtype=np.int64)
+    rows = np.zeros(m, dtype=np.int32)
+    cols = np.zeros(m, dtype=np.int32)
+    ab, abc, a32 = np.float32(a + b), np.float32(a + b + c), np.float32(a)
     for _level in range(scale):
         u = rng.random(m, dtype=np.float32)
-        rbit = u >= np.float32(a + b)
-        cbit = ((u >= np.float32(a)) & ~rbit) | (u >= np.float32(a + b + c))
-        rows = (rows << 1) | rbit
-        cols = (cols << 1) | cbit
+        rbit = u >= ab  # quadrants c, d: row bit set
+        cbit = u >= abc  # quadrant d ...
+        cbit |= (u >= a32) & ~rbit  # ... or quadrant b: column bit set
+        np.left_shift(rows, 1, out=rows)
+        np.left_shift(cols, 1, out=cols)
+        rows |= rbit
+        cols |= cbit
     return rows, cols
 
 

@@ -90,7 +90,8 @@ SPORDER_API void sporder_reorder(sporder_context_t ctx, int32_t n, int32_t nnz,
 SPORDER_API const char *sporder_last_error(void);
 
 /* Run the context's work on `stream` (a cudaStream_t) instead of the context's
- * private stream; NULL restores the private stream.  Calls stay synchronous. */
+ * private stream; NULL restores the private stream.  To name the legacy default
+ * stream pass cudaStreamLegacy ((cudaStream_t)0x1), not 0.  Calls stay synchronous. */
 SPORDER_API void sporder_context_set_stream(sporder_context_t ctx, void *stream);
 
 /* Bytes of device workspace the context currently holds (grow-only cache). */
@@ -108,6 +109,21 @@ SPORDER_API int32_t sporder_csg_with_table(sporder_context_t ctx, int32_t n, int
                                            uint64_t *d_table, uint64_t d_table_capacity,
                                            sporder_csg_timing_t *timing,
                                            sporder_csg_stats_t *stats);
+
+/* csg of one row shard: rows [row_base, row_base + n_rows) of a matrix with n_cols
+ * columns, given as a CSR block whose d_ptr is rebased to start at 0 and whose
+ * column ids are the matrix's own.  row_base must be a multiple of chunk_size so
+ * that the shard holds whole chunks; then its chunks see exactly the candidates
+ * they see in the full matrix and the results (d_new_order[i], table indices) are
+ * the full matrix's, already offset by row_base.  k and chunk_size should be
+ * passed resolved (k <= 0 would resolve from the shard's own nnz / n_rows).
+ * d_new_order and d_table may be NULL.  Returns k_used, or -1 on error. */
+SPORDER_API int32_t sporder_csg_shard(sporder_context_t ctx, int32_t n_rows, int32_t n_cols,
+                                      int32_t row_base, int32_t nnz, const int32_t *d_ptr,
+                                      const int32_t *d_ind, int32_t k, float oversampling,
+                                      int32_t chunk_size, int32_t *d_new_order,
+                                      uint64_t *d_table, uint64_t d_table_capacity,
+                                      sporder_csg_timing_t *timing, sporder_csg_stats_t *stats);
 
 /* csg on host buffers: copies ptr/ind to the device, reorders, copies the
  * permutation back.  Returns 0, or -1 on error. */

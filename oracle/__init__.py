@@ -88,15 +88,17 @@ def greedy(table, n, chunk_size):
 
 
 def csg(ptr, ind, is_symmetric=False, k=0, oversampling=0.0, chunk_size=0, with_table=False,
-        with_stats=False):
-    """Full pipeline.  Returns order [, table] [, stats dict]."""
+        with_stats=False, ncols=None):
+    """Full pipeline.  Returns order [, table] [, stats dict].  ``ncols`` > n runs a
+    block of whole chunks cut out of a wider matrix (pass k explicitly then)."""
     ptr, ind = _i32(ptr), _i32(ind)
     n, nnz = ptr.size - 1, ind.size
+    ncols = n if ncols is None else int(ncols)
     prm = resolve_params(n, nnz, k, oversampling, chunk_size)
     order = np.empty(n, dtype=np.int32)
     table = np.zeros((n, prm["k"]), dtype=np.uint64) if with_table else None
     st = CsgStats()
-    rc = lib().oracle_csg(C.c_int32(n), C.c_int32(nnz), _p(ptr), _p(ind),
+    rc = lib().oracle_csg_rect(C.c_int32(n), C.c_int32(ncols), C.c_int32(nnz), _p(ptr), _p(ind),
                           C.c_int(bool(is_symmetric)), C.c_int32(k), C.c_float(oversampling),
                           C.c_int32(chunk_size), _p(order), _p(table),
                           C.byref(st) if with_stats else None)

@@ -65,16 +65,20 @@ ORACLE_API int oracle_resolve_params(int32_t n, int32_t nnz, int32_t *k, float *
 
 /* ---- CSR -> CSC: sporder/src/common/csr2csc.cu:62-113 ----
  * (stable sort of row-major (col,row) pairs by column => rows ascending per column) */
-ORACLE_API void oracle_csr2csc(int32_t n, int32_t nnz, const int32_t *ptr, const int32_t *ind,
-                               int32_t *col_ptr, int32_t *row_ind) {
-  memset(col_ptr, 0, sizeof(int32_t) * ((size_t)n + 1));
+ORACLE_API void oracle_csr2csc_rect(int32_t n, int32_t ncols, int32_t nnz, const int32_t *ptr,
+                                    const int32_t *ind, int32_t *col_ptr, int32_t *row_ind) {
+  memset(col_ptr, 0, sizeof(int32_t) * ((size_t)ncols + 1));
   for (int32_t i = 0; i < nnz; ++i) col_ptr[ind[i] + 1]++;
-  for (int32_t c = 0; c < n; ++c) col_ptr[c + 1] += col_ptr[c];
-  int32_t *fill = (int32_t *)malloc(sizeof(int32_t) * ((size_t)n + 1));
-  memcpy(fill, col_ptr, sizeof(int32_t) * ((size_t)n + 1));
+  for (int32_t c = 0; c < ncols; ++c) col_ptr[c + 1] += col_ptr[c];
+  int32_t *fill = (int32_t *)malloc(sizeof(int32_t) * ((size_t)ncols + 1));
+  memcpy(fill, col_ptr, sizeof(int32_t) * ((size_t)ncols + 1));
   for (int32_t r = 0; r < n; ++r)
     for (int32_t p = ptr[r]; p < ptr[r + 1]; ++p) row_ind[fill[ind[p]]++] = r;
   free(fill);
+}
+ORACLE_API void oracle_csr2csc(int32_t n, int32_t nnz, const int32_t *ptr, const int32_t *ind,
+                               int32_t *col_ptr, int32_t *row_ind) {
+  oracle_csr2csc_rect(n, n, nnz, ptr, ind, col_ptr, row_ind);
 }
 
 /* ---- Space-Saving sketch of one row + top-k selection ----
@@ -198,18 +202,23 @@ static void sketch_row(int32_t r, int32_t n, int32_t k, int32_t chunk, int32_t M
 /* ---- top-k table for all rows: chunk_similarity_top_k.cu:137-154 ----
  * table[n*k] packed entries; unused entries are zero.  col_ptr/row_ind are the
  * CSC (or the CSR itself when the caller promised symmetry: csr2csc.h:52-54). */
-ORACLE_API int oracle_csg_table(int32_t n, int32_t nnz, const int32_t *ptr, const int32_t *ind,
-                                int is_symmetric, int32_t k, float ovs, int32_t chunk,
-                                uint64_t *table) {
+/* ncols > n describes a block of whole chunks cut out of a larger matrix (rows
+ * renumbered from 0, columns kept): every chunk of the block sees exactly the
+ * candidates it sees inside the full matrix, because candidates never leave a
+ * chunk.  Used for row shards and for the bounded samples of the CPU baseline. */
+ORACLE_API int oracle_csg_table_rect(int32_t n, int32_t ncols, int32_t nnz, const int32_t *ptr,
+                                     const int32_t *ind, int is_symmetric, int32_t k, float ovs,
+                                     int32_t chunk, uint64_t *table) {
   int32_t m_used, M;
-  if (n < 1) return 3;
+  if (n < 1 || ncols < n) return 3;
+  if (is_symmetric && ncols != n) return 3;
   if (oracle_resolve_params(n, nnz, &k, &ovs, &chunk, &m_used, &M)) return 1;
   int32_t *col_ptr = NULL, *row_ind = NULL;
   const int32_t *cp = ptr, *ri = ind;
   if (!is_symmetric) {
-    col_ptr = (int32_t *)malloc(sizeof(int32_t) * ((size_t)n + 1));
+    col_ptr = (int32_t *)malloc(sizeof(int32_t) * ((size_t)ncols + 1));
     row_ind = (int32_t *)malloc(sizeof(int32_t) * ((size_t)(nnz > 0 ? nnz : 1)));
-    oracle_csr2csc(n, nnz, ptr, ind, col_ptr, row_ind);
+    oracle_csr2csc_rect(n, ncols, nnz, ptr, ind, col_ptr, row_ind);
     cp = col_ptr;
     ri = row_ind;
   }
@@ -231,6 +240,12 @@ ORACLE_API int oracle_csg_table(int32_t n, int32_t nnz, const int32_t *ptr, cons
   free(col_ptr);
   free(row_ind);
   return 0;
+}
+
+ORACLE_API int oracle_csg_table(int32_t n, int32_t nnz, const int32_t *ptr, const int32_t *ind,
+                                int is_symmetric, int32_t k, float ovs, int32_t chunk,
+                                uint64_t *table) {
+  return oracle_csg_table_rect(n, n, nnz, ptr, ind, is_symmetric, k, ovs, chunk, table);
 }
 
 /* ---- greedy chain per chunk: sporder/src/csg/chunk_similarity_greedy.cu:14-96,
@@ -327,15 +342,16 @@ typedef struct {
 /* ---- whole pipeline: sporder.cpp:140-166 + chunk_similarity_greedy.cu:100-138 ----
  * table_out (may be NULL) receives the n*k_used table; stats may be NULL.
  * returns 0, or nonzero where the reference would abort. */
-ORACLE_API int oracle_csg(int32_t n, int32_t nnz, const int32_t *ptr, const int32_t *ind,
-                          int is_symmetric, int32_t k, float ovs, int32_t chunk,
-                          int32_t *new_order, uint64_t *table_out, oracle_csg_stats_t *stats) {
+ORACLE_API int oracle_csg_rect(int32_t n, int32_t ncols, int32_t nnz, const int32_t *ptr,
+                               const int32_t *ind, int is_symmetric, int32_t k, float ovs,
+                               int32_t chunk, int32_t *new_order, uint64_t *table_out,
+                               oracle_csg_stats_t *stats) {
   int32_t m_used, M;
   if (n < 1) return 3;
   if (oracle_resolve_params(n, nnz, &k, &ovs, &chunk, &m_used, &M)) return 1;
   uint64_t *table = table_out;
   if (!table) table = (uint64_t *)malloc(sizeof(uint64_t) * (size_t)n * (size_t)k);
-  int rc = oracle_csg_table(n, nnz, ptr, ind, is_symmetric, k, ovs, chunk, table);
+  int rc = oracle_csg_table_rect(n, ncols, nnz, ptr, ind, is_symmetric, k, ovs, chunk, table);
   if (rc) {
     if (!table_out) free(table);
     return rc;
@@ -359,6 +375,13 @@ ORACLE_API int oracle_csg(int32_t n, int32_t nnz, const int32_t *ptr, const int3
   }
   if (!table_out) free(table);
   return 0;
+}
+
+ORACLE_API int oracle_csg(int32_t n, int32_t nnz, const int32_t *ptr, const int32_t *ind,
+                          int is_symmetric, int32_t k, float ovs, int32_t chunk,
+                          int32_t *new_order, uint64_t *table_out, oracle_csg_stats_t *stats) {
+  return oracle_csg_rect(n, n, nnz, ptr, ind, is_symmetric, k, ovs, chunk, new_order, table_out,
+                         stats);
 }
 
 /* ---- permutation application: sporder/src/reorder.cu:72-149 ----

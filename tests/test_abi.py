@@ -1,0 +1,57 @@
+"""The C-ABI library loads and exports every symbol include/sporder_b200.h declares.
+No compute calls: this runs without a GPU."""
+import ctypes
+import os
+import re
+
+from chunkedgreedy_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "sporder_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sporder_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(built_lib):
+    lib = ctypes.CDLL(built_lib)
+    declared = _declared_symbols()
+    assert len(declared) >= 12
+    for name in declared:
+        assert hasattr(lib, name), name
+
+
+def test_binding_table_covers_header(built_lib):
+    assert sorted(_lib.SYMBOLS) == _declared_symbols()
+    _lib.load()
+
+
+def test_struct_layouts_match_reference_header():
+    # sporder/include/sporder.h:203-222: timing = double + 3 floats, stats = 48 bytes
+    assert ctypes.sizeof(_lib.CsgTiming) == 24
+    assert ctypes.sizeof(_lib.CsgStats) == 48
+    assert _lib.CsgStats.avg_degree.offset == 8
+    assert _lib.CsgStats.zero_degree_rows.offset == 24
+    assert _lib.CsgStats.avg_followed_weight.offset == 40
+
+
+def test_null_context_is_an_error_not_a_crash(built_lib):
+    lib = _lib.load()
+    lib.sporder_chunk_similarity_greedy(None, 1, 0, None, None, False, 0, 0.0, 0, None, None, None)
+    assert _lib.last_error() == "null context"
+    assert lib.sporder_spmm(None, 1, 0, 1, None, None, None, None, None) == -1
+
+
+def test_no_cpu_fallback_message(monkeypatch):
+    import chunkedgreedy_b200 as sp
+    import torch
+    if torch.cuda.is_available():
+        return
+    try:
+        sp.Context()
+    except RuntimeError as e:
+        assert "no CPU fallback" in str(e)
+    else:
+        raise AssertionError("Context() must fail without a CUDA device")

@@ -1,0 +1,218 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU oracle, the
+committed reference outputs and (when its build travelled with the repository) the
+reference's own CUDA library.  Bit-exact for tables, permutations and reordered
+matrices; SpMM within 1e-5 of the fp64 product, scaled by sum_j |a_ij * b_jl|."""
+import hashlib
+
+import numpy as np
+import pytest
+
+import cases
+import oracle
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+def _sp():
+    import chunkedgreedy_b200 as sp
+    return sp
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _sha(a):
+    return np.frombuffer(hashlib.sha256(np.ascontiguousarray(a).tobytes()).digest(), dtype=np.uint8)
+
+
+@pytest.mark.parametrize("name", list(cases.CASES))
+def test_csg_matches_reference_outputs_and_oracle(name, golden):
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build(name)
+    order, table = sp.csg_table(_dev(ptr), _dev(ind), is_symmetric=sym, **params)
+    order, table = order.cpu().numpy(), table.cpu().numpy().view(np.uint64)
+    o_or, t_or = oracle.csg(ptr, ind, sym, with_table=True, **params)
+    assert np.array_equal(table, t_or)
+    assert np.array_equal(order, o_or)
+    assert np.array_equal(order, golden[name + "/order"])
+    assert np.array_equal(_sha(table), golden[name + "/table_sha256"])
+    plain = sp.chunk_similarity_greedy(_dev(ptr), _dev(ind), is_symmetric=sym, **params)
+    assert np.array_equal(plain.cpu().numpy(), o_or)
+
+
+@pytest.mark.parametrize("name", list(cases.BIG_CASES))
+def test_csg_larger_cases_against_oracle(name):
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build(name)
+    order, table = sp.csg_table(_dev(ptr), _dev(ind), is_symmetric=sym, **params)
+    o_or, t_or = oracle.csg(ptr, ind, sym, with_table=True, **params)
+    assert np.array_equal(table.cpu().numpy().view(np.uint64), t_or)
+    assert np.array_equal(order.cpu().numpy(), o_or)
+
+
+@pytest.mark.parametrize("name", ["hubsym", "rmat12", "m512", "bigchunk", "rmat16"])
+def test_csg_against_reference_library(name):
+    from oracle import ref
+    if not ref.available():
+        pytest.skip("reference build (oracle/_ref) not present")
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build(name)
+    dp, di = _dev(ptr), _dev(ind)
+    prm = oracle.resolve_params(ptr.size - 1, ind.size, **params)
+    order, table = sp.csg_table(dp, di, is_symmetric=sym, **params)
+    r_order = ref.csg(dp, di, sym, **params)
+    r_table = ref.csg_table(dp, di, sym, prm["k"], prm["oversampling"], prm["chunk_size"])
+    assert torch.equal(table, r_table)
+    assert torch.equal(order, r_order)
+
+
+@pytest.mark.parametrize("name", ["band1000", "ragged", "hubsym", "zipf4k", "rmat12", "rmat16"])
+@pytest.mark.parametrize("symmetric", [False, True])
+def test_reorder_bit_exact(name, symmetric, golden):
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build(name)
+    order = oracle.csg(ptr, ind, sym, **params)
+    rp, ri, rv = oracle.reorder(ptr, ind, order, val, symmetric=symmetric)
+    gp, gi, gv = sp.reorder(_dev(ptr), _dev(ind), _dev(order), val=_dev(val), symmetric=symmetric)
+    assert np.array_equal(gp.cpu().numpy(), rp)
+    assert np.array_equal(gi.cpu().numpy(), ri)
+    assert np.array_equal(gv.cpu().numpy(), rv)
+    gp2, gi2 = sp.reorder(_dev(ptr), _dev(ind), _dev(order), symmetric=symmetric)
+    assert np.array_equal(gi2.cpu().numpy(), ri) and np.array_equal(gp2.cpu().numpy(), rp)
+    if symmetric and name in cases.CASES:
+        assert np.array_equal(gp.cpu().numpy(), golden[name + "/sym_ptr"])
+        assert np.array_equal(_sha(gi.cpu().numpy()), golden[name + "/sym_ind_sha256"])
+        assert np.array_equal(_sha(gv.cpu().numpy()), golden[name + "/sym_val_sha256"])
+
+
+def test_reorder_random_permutation_long_rows():
+    # rows of every size class: <= 32 (warp), <= 2048 (shared memory), longer (global)
+    sp = _sp()
+    rng = np.random.default_rng(3)
+    n = 6000
+    lens = np.concatenate([rng.integers(0, 33, 5900), rng.integers(33, 2049, 90),
+                           rng.integers(2049, 5000, 10)])
+    rng.shuffle(lens)
+    rows = np.repeat(np.arange(n), lens)
+    cols = np.concatenate([rng.choice(n, l, replace=False) for l in lens])
+    from chunkedgreedy_b200.synth import coo_to_csr
+    ptr, ind, val = coo_to_csr(n, rows, cols, rng.standard_normal(rows.size))
+    order = rng.permutation(n).astype(np.int32)
+    for symmetric in (False, True):
+        rp, ri, rv = oracle.reorder(ptr, ind, order, val, symmetric=symmetric)
+        gp, gi, gv = sp.reorder(_dev(ptr), _dev(ind), _dev(order), val=_dev(val),
+                                symmetric=symmetric)
+        assert np.array_equal(gp.cpu().numpy(), rp)
+        assert np.array_equal(gi.cpu().numpy(), ri)
+        assert np.array_equal(gv.cpu().numpy(), rv)
+
+
+def test_reorder_round_trip_is_identity():
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build("rmat12")
+    order = sp.chunk_similarity_greedy(_dev(ptr), _dev(ind))
+    p1, i1, v1 = sp.reorder(_dev(ptr), _dev(ind), order, val=_dev(val), symmetric=True)
+    inv = torch.empty_like(order)
+    inv[order.long()] = torch.arange(order.numel(), dtype=torch.int32, device="cuda")
+    p2, i2, v2 = sp.reorder(p1, i1, inv, val=v1, symmetric=True)
+    assert np.array_equal(p2.cpu().numpy(), ptr) and np.array_equal(i2.cpu().numpy(), ind)
+    assert np.array_equal(v2.cpu().numpy(), val)
+
+
+@pytest.mark.parametrize("name", ["band1000", "zipf4k", "rmat12", "rmat16", "ragged"])
+@pytest.mark.parametrize("w", [1, 7, 16, 32, 64, 128, 256])
+def test_spmm_within_1e5_of_fp64(name, w):
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build(name)
+    n = ptr.size - 1
+    B = np.random.default_rng(42).standard_normal((n, w)).astype(np.float32)
+    C = sp.spmm(_dev(ptr), _dev(ind), _dev(val), _dev(B)).cpu().numpy()
+    ref64, refabs = oracle.spmm_f64(ptr, ind, val, B)
+    # tolerance stated by the workload definition: 1e-5 relative, scaled by sum |a*b|
+    assert np.all(np.abs(C - ref64) <= 1e-5 * refabs + 1e-30)
+
+
+def test_spmm_is_linear_and_permutation_consistent():
+    # size-independent properties at a larger size: A(x+y) = Ax + Ay, and
+    # (P A P^T)(P x) = P (A x)
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build("rmat16")
+    n = ptr.size - 1
+    dp, di, dv = _dev(ptr), _dev(ind), _dev(val)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn((n, 32), device="cuda", generator=g)
+    y = torch.randn((n, 32), device="cuda", generator=g)
+    ax, ay, axy = sp.spmm(dp, di, dv, x), sp.spmm(dp, di, dv, y), sp.spmm(dp, di, dv, x + y)
+    scale = sp.spmm(dp, di, dv.abs(), x.abs() + y.abs())
+    assert torch.all((axy - ax - ay).abs() <= 1e-5 * scale + 1e-30)
+    order = sp.chunk_similarity_greedy(dp, di)
+    p2, i2, v2 = sp.reorder(dp, di, order, val=dv, symmetric=True)
+    lhs = sp.spmm(p2, i2, v2, x[order.long()])
+    assert torch.all((lhs - ax[order.long()]).abs() <= 1e-5 * scale[order.long()] + 1e-30)
+
+
+def test_stats_and_timing_fields():
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build("rmat12")
+    order, timing, stats = sp.chunk_similarity_greedy(_dev(ptr), _dev(ind), with_timing=True,
+                                                      with_stats=True)
+    o_or, s_or = oracle.csg(ptr, ind, sym, with_stats=True)
+    assert np.array_equal(order.cpu().numpy(), o_or)
+    assert set(timing) == {"wall_ms", "csr2csc_ms", "similarity_ms", "chunk_greedy_ms"}
+    assert timing["wall_ms"] > 0
+    for key in ("k_used", "m_used", "zero_degree_rows", "chunk_size_used", "chain_restarts"):
+        assert stats[key] == s_or[key], key
+    for key in ("avg_degree", "avg_edge_weight", "avg_followed_weight"):
+        assert abs(stats[key] - s_or[key]) <= 1e-6 * max(1.0, abs(s_or[key])), key
+    only_stats = sp.chunk_similarity_greedy(_dev(ptr), _dev(ind), with_stats=True)
+    assert isinstance(only_stats, tuple) and len(only_stats) == 2 and "k_used" in only_stats[1]
+
+
+def test_errors_are_exceptions_and_context_survives():
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build("uniform")
+    dp, di = _dev(ptr), _dev(ind)
+    with pytest.raises(ValueError):
+        sp.chunk_similarity_greedy(dp, di, k=200, oversampling=4.0)  # m = 800 > 512
+    with pytest.raises(ValueError):
+        sp.chunk_similarity_greedy(dp, di, oversampling=0.5)
+    with pytest.raises(ValueError):
+        sp.chunk_similarity_greedy(dp[:1], di)
+    with pytest.raises(ValueError):
+        sp.reorder(dp, di, dp[:5])
+    with pytest.raises(ValueError):
+        sp.chunk_similarity_greedy(dp.long(), di)
+    order = sp.chunk_similarity_greedy(dp, di)  # still works after the failures
+    assert np.array_equal(order.cpu().numpy(), oracle.csg(ptr, ind, sym))
+
+
+def test_result_independent_of_repeat_and_context():
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build("rmat12")
+    dp, di = _dev(ptr), _dev(ind)
+    a = sp.chunk_similarity_greedy(dp, di)
+    ctx = sp.Context()
+    b = sp.chunk_similarity_greedy(dp, di, ctx=ctx)
+    c = sp.chunk_similarity_greedy(dp, di, ctx=ctx)
+    assert torch.equal(a, b) and torch.equal(b, c)
+    ctx.close()
+
+
+def test_host_entry_point_matches_device_path():
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build("rmat12")
+    hp, hi = torch.from_numpy(ptr).pin_memory(), torch.from_numpy(ind).pin_memory()
+    out = sp.chunk_similarity_greedy_host(hp, hi)
+    assert np.array_equal(out.numpy(), oracle.csg(ptr, ind, sym))
+
+
+def test_native_library_is_the_one_that_ran():
+    sp = _sp()
+    before = sp.kernel_launches()
+    ptr, ind, val, sym, params = cases.build("uniform")
+    sp.chunk_similarity_greedy(_dev(ptr), _dev(ind))
+    assert sp.kernel_launches() >= before + 5
+    maps = open("/proc/self/maps").read()
+    assert "libsporder_b200.so" in maps
