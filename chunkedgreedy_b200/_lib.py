@@ -50,6 +50,7 @@ SYMBOLS = {
                                                          C.POINTER(CsgStats)]),
     "sporder_spmm": (C.c_int32, [_P, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P]),
     "sporder_spmm_async": (C.c_int32, [_P, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P]),
+    "sporder_spmm_static": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P]),
     "sporder_kernel_launches": (C.c_uint64, []),
 }
 

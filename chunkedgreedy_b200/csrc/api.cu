@@ -25,7 +25,7 @@ void set_error(const char *fmt, ...) {
   g_has_err = true;
 }
 bool has_error() { return g_has_err; }
-static void clear_error() { g_has_err = false; }
+void clear_error() { g_has_err = false; }
 void count_launches(int k) { g_launches.fetch_add(static_cast<uint64_t>(k), std::memory_order_relaxed); }
 
 bool ensure_workspace(Context &ctx, size_t bytes) {

@@ -15,6 +15,7 @@ namespace csg {
 // library records the message per thread and returns instead.
 void set_error(const char *fmt, ...);
 bool has_error();
+void clear_error();
 void count_launches(int k);  // feeds sporder_kernel_launches()
 
 #define CSG_CUDA(call)                                                                  \

@@ -13,6 +13,9 @@
 // warp therefore handles 32/G row pieces at once.  Rows longer than SPLIT are cut
 // into pieces that are added with atomics (C is zeroed first for those rows), so a
 // hub row never serialises on one warp.
+#include <mutex>
+
+#include "../../include/sporder_b200.h"
 #include "common.cuh"
 
 namespace csg {
@@ -200,3 +203,96 @@ bool launch_spmm(Context &ctx, int32_t n, int32_t nnz, int32_t w, const int32_t 
 }
 
 }  // namespace csg
+
+// ---------------------------------------------------------------------------------
+// SpMM without any allocation.
+//
+// Some hosts of this library must not see a cudaMalloc from it: applications that
+// have handed all device memory to an allocator of their own (a tensor framework's
+// caching pool run with a fixed memory share, a database buffer pool), where a
+// driver allocation inside a library call can fail outright or push the process
+// over its budget; and request paths that ban driver allocations because
+// cudaMalloc / cudaFree stall every stream of the device.  For them the queue of
+// long rows -- the only scratch the SpMM kernels need -- lives in a fixed array
+// that is part of the loaded library image, so every GPU that loads the library
+// holds these 256 KiB until the process exits.
+//
+// The array is shared by every call in the process and keeps what the last call
+// left in it; the call clears the one counter that must start at zero.  Two calls
+// whose kernels can overlap on the same GPU (different streams) would race on it.
+namespace csg {
+namespace {
+
+constexpr int STATIC_MAX_LONG_ROWS = 65536;  // queue capacity
+constexpr int STATIC_QUEUE_OFFSET = 64;      // words; the counter owns the first 256 bytes
+static __device__ __align__(256) uint32_t g_spmm_static_scratch[STATIC_QUEUE_OFFSET +
+                                                                STATIC_MAX_LONG_ROWS];
+
+// In host code the symbol above is only a stand-in, not a device address: the real
+// address is asked for once per device, with that device current.
+constexpr int MAX_DEVICES = 64;
+std::mutex g_static_mutex;
+uint32_t *g_static_addr[MAX_DEVICES] = {};
+
+bool static_scratch_address(int device, uint32_t **out) {
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  CSG_REQUIRE(device >= 0 && device < MAX_DEVICES, "spmm_static: device %d out of range", device);
+  if (!g_static_addr[device]) {
+    void *p = nullptr;
+    CSG_CUDA(cudaGetSymbolAddress(&p, g_spmm_static_scratch));
+    g_static_addr[device] = static_cast<uint32_t *>(p);
+  }
+  *out = g_static_addr[device];
+  return true;
+}
+
+bool run_spmm_static(int32_t n, int32_t nnz, int32_t w, const int32_t *d_ptr, const int32_t *d_ind,
+                     const float *d_val, const float *d_B, float *d_C, cudaStream_t stream) {
+  CSG_REQUIRE(n >= 1 && nnz >= 0 && w >= 1, "spmm_static: bad sizes n=%d nnz=%d w=%d", n, nnz, w);
+  CSG_REQUIRE(d_ptr && d_B && d_C && (nnz == 0 || (d_ind && d_val)), "spmm_static: null array");
+  // at most nnz / SPLIT rows can be longer than SPLIT; all of them must fit the queue
+  CSG_REQUIRE(static_cast<int64_t>(nnz) / SPLIT + 1 <= STATIC_MAX_LONG_ROWS,
+              "spmm_static: nnz = %d exceeds the fixed scratch (at most %lld nonzeros); use sporder_spmm",
+              nnz, static_cast<long long>(STATIC_MAX_LONG_ROWS - 1) * SPLIT + SPLIT - 1);
+  Context tmp;  // stack object only: stream and SM count for the launch geometry
+  CSG_CUDA(cudaGetDevice(&tmp.device));
+  CSG_CUDA(cudaDeviceGetAttribute(&tmp.num_sms, cudaDevAttrMultiProcessorCount, tmp.device));
+  tmp.stream = stream;
+  uint32_t *scratch = nullptr;
+  if (!static_scratch_address(tmp.device, &scratch)) return false;
+  SpmmArgs a;
+  a.n = n;
+  a.w = w;
+  a.ptr = d_ptr;
+  a.ind = d_ind;
+  a.val = d_val;
+  a.B = d_B;
+  a.C = d_C;
+  a.long_count = scratch;
+  a.long_rows = reinterpret_cast<int32_t *>(scratch + STATIC_QUEUE_OFFSET);
+  CSG_CUDA(cudaMemsetAsync(a.long_count, 0, sizeof(uint32_t), stream));  // last call's count
+  const bool al16 = (reinterpret_cast<uintptr_t>(d_B) % 16 == 0) &&
+                    (reinterpret_cast<uintptr_t>(d_C) % 16 == 0);
+  if (w % 128 == 0 && al16) return launch_variant<32, 4>(tmp, a);
+  if (w % 64 == 0 && al16) return launch_variant<16, 4>(tmp, a);
+  if (w % 32 == 0 && al16) return launch_variant<8, 4>(tmp, a);
+  if (w % 16 == 0 && al16) return launch_variant<4, 4>(tmp, a);
+  if (w % 32 == 0) return launch_variant<32, 1>(tmp, a);
+  if (w % 8 == 0) return launch_variant<8, 1>(tmp, a);
+  if (w % 4 == 0) return launch_variant<4, 1>(tmp, a);
+  if (w % 2 == 0) return launch_variant<2, 1>(tmp, a);
+  return launch_variant<1, 1>(tmp, a);
+}
+
+}  // namespace
+}  // namespace csg
+
+extern "C" int32_t sporder_spmm_static(int32_t n, int32_t nnz, int32_t w, const int32_t *d_ptr,
+                                       const int32_t *d_ind, const float *d_val, const float *d_B,
+                                       float *d_C, void *stream) {
+  csg::clear_error();
+  return csg::run_spmm_static(n, nnz, w, d_ptr, d_ind, d_val, d_B, d_C,
+                              static_cast<cudaStream_t>(stream))
+             ? 0
+             : -1;
+}

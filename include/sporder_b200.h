@@ -146,6 +146,24 @@ SPORDER_API int32_t sporder_spmm_async(sporder_context_t ctx, int32_t n, int32_t
                                        const int32_t *d_ptr, const int32_t *d_ind,
                                        const float *d_val, const float *d_B, float *d_C);
 
+/* SpMM for callers that must not trigger a device allocation (no counterpart in the
+ * reference).  Same product as sporder_spmm, but it takes no context and calls no
+ * cudaMalloc / cudaFree or allocating routine: the queue of long rows sits in a fixed
+ * 256 KiB array inside the library image (held by every GPU that loads the library
+ * until the process exits).  Meant for hosts that gave all device memory to their own
+ * pool, or that ban driver allocations on their request path because those stall the
+ * whole device.
+ *   - limit: nnz < 65536 * 1024 (67,108,864); larger inputs are rejected with an error;
+ *   - the work is queued on `stream` (a cudaStream_t; NULL = default stream) and the
+ *     call returns without waiting for it;
+ *   - the first call on each device looks up the array's device address; make that
+ *     first call before any stream capture;
+ *   - all calls share the array: calls whose kernels may overlap on one GPU race.
+ * Returns 0, or -1 on error (see sporder_last_error). */
+SPORDER_API int32_t sporder_spmm_static(int32_t n, int32_t nnz, int32_t w, const int32_t *d_ptr,
+                                        const int32_t *d_ind, const float *d_val,
+                                        const float *d_B, float *d_C, void *stream);
+
 /* Number of kernels this library has launched in this process (all contexts). */
 SPORDER_API uint64_t sporder_kernel_launches(void);
 
