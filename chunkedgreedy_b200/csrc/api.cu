@@ -103,12 +103,19 @@ bool plan_scratch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, uint
   const size_t z = static_cast<size_t>(nnz > 0 ? nnz : 1);
   const size_t o_keyA = ar.take(4 * z), o_keyB = ar.take(4 * z);
   const size_t o_payA = ar.take(4 * z), o_payB = ar.take(4 * z);
-  const size_t o_cand = ar.take(8 * z), o_seg = ar.take(8 * z);
+  const size_t o_cand = ar.take(8 * z), o_seg = ar.take(8 * z), o_rank = ar.take(4 * z);
   const size_t o_work = ar.take(4 * static_cast<size_t>(n));
   const size_t o_list = ar.take(4 * static_cast<size_t>(n));
   const size_t o_ctrl = ar.take(4 * CTRL_WORDS);
   const size_t bw = greedy_bitmap_words(n, p.chunk);
   const size_t o_bm = ar.take(4 * (bw ? bw : 1));
+  // heavy chunks hold more than 15360 nonzeros each and are cut into tiles of 4096
+  const size_t chunks = (static_cast<size_t>(n) + p.chunk - 1) / p.chunk;
+  size_t heavy_max = z / 15360 + 1;
+  if (heavy_max > chunks) heavy_max = chunks;
+  const size_t tiles_max = z / 4096 + heavy_max + 1;
+  const size_t o_hc = ar.take(4 * heavy_max), o_htb = ar.take(4 * (heavy_max + 1));
+  const size_t o_th = ar.take(4 * 256 * tiles_max), o_db = ar.take(4 * 256 * heavy_max);
   const size_t o_table = user_table ? 0 : ar.take(8 * static_cast<size_t>(n) * p.k);
   if (!ensure_workspace(ctx, ar.off)) return false;
   s->keyA = reinterpret_cast<uint32_t *>(ctx.ws + o_keyA);
@@ -117,10 +124,15 @@ bool plan_scratch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, uint
   s->payB = reinterpret_cast<uint32_t *>(ctx.ws + o_payB);
   s->cand = reinterpret_cast<int2 *>(ctx.ws + o_cand);
   s->seg = reinterpret_cast<int2 *>(ctx.ws + o_seg);
+  s->seg_rank = reinterpret_cast<int32_t *>(ctx.ws + o_rank);
   s->row_work = reinterpret_cast<uint32_t *>(ctx.ws + o_work);
   s->row_list = reinterpret_cast<int32_t *>(ctx.ws + o_list);
   s->ctrl = reinterpret_cast<uint32_t *>(ctx.ws + o_ctrl);
   s->table = user_table ? user_table : reinterpret_cast<uint64_t *>(ctx.ws + o_table);
+  s->heavy_chunk = reinterpret_cast<int32_t *>(ctx.ws + o_hc);
+  s->heavy_tile_base = reinterpret_cast<int32_t *>(ctx.ws + o_htb);
+  s->tile_hist = reinterpret_cast<uint32_t *>(ctx.ws + o_th);
+  s->digit_base = reinterpret_cast<uint32_t *>(ctx.ws + o_db);
   s->gbitmaps = bw ? reinterpret_cast<uint32_t *>(ctx.ws + o_bm) : nullptr;
   return true;
 }
@@ -215,6 +227,8 @@ sporder_context_t sporder_context_create(void) {
   if ((e = cudaStreamCreateWithFlags(&c.own_stream, cudaStreamNonBlocking)) != cudaSuccess)
     return fail(e, "cudaStreamCreate");
   c.stream = c.own_stream;
+  if ((e = cudaStreamCreateWithFlags(&c.aux_stream, cudaStreamNonBlocking)) != cudaSuccess)
+    return fail(e, "cudaStreamCreate");
   cudaDeviceGetAttribute(&c.num_sms, cudaDevAttrMultiProcessorCount, c.device);
   cudaDeviceGetAttribute(&c.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, c.device);
   for (auto &ev : c.ev)
@@ -233,6 +247,7 @@ void sporder_context_destroy(sporder_context_t h) {
   for (auto &ev : c.ev)
     if (ev) cudaEventDestroy(ev);
   if (c.h_pinned) cudaFreeHost(c.h_pinned);
+  if (c.aux_stream) cudaStreamDestroy(c.aux_stream);
   if (c.own_stream) cudaStreamDestroy(c.own_stream);
   delete h;
 }

@@ -44,6 +44,7 @@ struct Context {
   int device = 0;
   cudaStream_t stream = nullptr;  // stream every launch of this context uses
   cudaStream_t own_stream = nullptr;
+  cudaStream_t aux_stream = nullptr;  // helper stream for work that runs beside `stream`
   int num_sms = 0;
   int smem_optin = 0;  // max dynamic shared memory per block (opt-in)
   char *ws = nullptr;  // device workspace
@@ -80,24 +81,34 @@ struct CsgScratch {
   uint32_t *keyA, *keyB, *payA, *payB;  // ping-pong buffers of the global sort path
   int2 *cand;                           // (row, row length) grouped by (chunk, column), rows ascending
   int2 *seg;                            // per nonzero: (first index into cand, group length)
+  int32_t *seg_rank;                    // per nonzero: index of its own row inside that group
   uint32_t *row_work;                   // candidates each row will see
   // work list of rows with candidates, heaviest bucket first
   int32_t *row_list;
   uint32_t *ctrl;  // [0]=chunk ticket [1]=row ticket [2]=rows listed [3..] see CTRL_* below
   uint64_t *table;  // n*k packed top-k entries
   uint32_t *gbitmaps;  // greedy bitmaps when they do not fit shared memory, else nullptr
+  // tiled sort of heavy chunks (see transpose.cu)
+  int32_t *heavy_chunk, *heavy_tile_base;
+  uint32_t *tile_hist, *digit_base;
 };
 enum {
   CTRL_CHUNK_TICKET = 0,
   CTRL_ROW_TICKET = 1,
   CTRL_ROWS_LISTED = 2,
   CTRL_BAD_INPUT = 3,      // set by a kernel that met row pointers outside [0, nnz]
+  CTRL_HEAVY_COUNT = 4,    // chunks sorted by the tiled path
+  CTRL_HEAVY_TILES = 5,    // their tiles
+  CTRL_HEAVY_ROWS = 6,     // rows at the head of row_list that the heavy sketch kernel takes
+  CTRL_HEAVY_TICKET = 7,
   CTRL_BUCKET_COUNT = 8,   // 33 entries
   CTRL_BUCKET_BASE = 48,   // 33 entries
   CTRL_BUCKET_FILL = 88,   // 33 entries
   CTRL_STATS = 128,        // see stats.cu
   CTRL_WORDS = 160
 };
+
+constexpr int SKETCH_HEAVY_BUCKET = 17;  // rows streaming >= 65536 candidates are "heavy"
 
 // stage launchers; all enqueue on ctx.stream and return false after set_error()
 bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32_t chunk, const int32_t *d_ptr,

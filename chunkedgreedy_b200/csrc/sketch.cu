@@ -12,36 +12,62 @@
 //   top-k         :46-66,71-90 (per-lane selection sort by weight, then k rounds
 //                 of arg-max over the lanes' cursors, ties to the smaller lane)
 //
-// What differs is the machinery.  The candidate stream comes from the chunk-local
-// transpose (coalesced, no out-of-chunk entries), rows are taken from a work list
-// ordered heaviest first (the stream of one row is inherently sequential, so the
-// longest rows must start first), and a sketch step costs one vote plus, on a miss
-// with a full sketch, two warp reductions (redux.sync) instead of ten shuffles.
+// What differs is the machinery.  One warp consumes one row's stream, as in the
+// reference, but
+//  * rows come from a work list ordered heaviest first: the stream of one row is an
+//    order-dependent chain, so the longest rows must start first;
+//  * stream elements are PRODUCED in batches into shared memory - lane-parallel over the
+//    column groups of the chunk-local transpose, coalesced for long groups, Dice terms
+//    computed here - and CONSUMED from there in a tight loop, so group bookkeeping,
+//    address arithmetic, the divide and DRAM latency stay out of the dependent chain;
+//  * a step on a full sketch costs three redux.sync (the cheapest warp collective on
+//    this part): one hit test and two for the eviction victim of the NEXT miss, which
+//    is computed ahead of time from each lane's cached two smallest weights (see
+//    Sketch::add_full);
+//  * the rows with the longest streams set the run time of the whole call, and a warp
+//    that shares its scheduler with seven others takes 1.6x longer per step.  Those
+//    rows therefore go to a kernel of their own (sketch_heavy_kernel): one block per
+//    SM holding all of its shared memory, so nothing else is scheduled there, and in
+//    it a producer warp and a consumer warp per row, double-buffered through shared
+//    memory.  All other rows run beside it, on another stream, at full occupancy with
+//    one warp doing both jobs.
 #include "common.cuh"
 
 namespace csg {
 
 namespace {
 
-constexpr int S_THREADS = 128;
+constexpr int S_WARPS = 4;
+constexpr int S_THREADS = 32 * S_WARPS;
+constexpr int S_RING = 256;    // stream elements per batch, light rows
+constexpr int H_RING = 512;    // stream elements per buffer, heavy rows (two buffers per row)
+constexpr int S_LONG = 48;     // groups with at least this many pending entries are copied by the whole warp
 
 struct SketchArgs {
-  int32_t n, nnz, k, row_base;
+  int32_t n, nnz, k, row_base, chunk;
   const int32_t *ptr;
   const int2 *seg;
+  const int32_t *seg_rank;
   const int2 *cand;
   const int32_t *row_list;
+  const uint32_t *row_work;
   uint32_t *ctrl;
   uint64_t *table;
 };
 
-// The sketch of one row: CELLS slots per lane.  Slot (lane, cell) is the
-// (lane*CELLS + cell)-th to be filled.
+// The sketch of one row: CELLS slots per lane, all in registers.  Slot (lane, cell) is
+// the (lane*CELLS + cell)-th to be filled; its number is lane*CELLS + cell.
 template <int CELLS>
 struct Sketch {
   int32_t key[CELLS];
   float w[CELLS];
-  int32_t filled;  // warp-uniform
+  int32_t filled;      // warp-uniform
+  // valid while the sketch is full:
+  uint32_t gmin;       // weight bits of the slot the next miss evicts (same in all lanes)
+  int32_t gown;        // its lane
+  int32_t gcell;       // its cell
+  uint32_t l1w, l2w;   // this lane's smallest and second smallest weight (bits) ...
+  int32_t l1c, l2c;    // ... and their cells, ordered by (weight, cell)
 
   __device__ __forceinline__ void clear() {
 #pragma unroll
@@ -50,57 +76,123 @@ struct Sketch {
       w[c] = 0.0f;
     }
     filled = 0;
+    gmin = 0;
+    gown = gcell = 0;
+    l1w = l2w = 0;
+    l1c = l2c = 0;
   }
 
-  // one stream element, all lanes hold the same (s, a)
-  __device__ __forceinline__ void add(int32_t s, float a) {
-    bool hit = false;
-#pragma unroll
-    for (int c = 0; c < CELLS; ++c) {
-      if (key[c] == s) {
-        w[c] += a;
-        hit = true;
-      }
-    }
-    if (__any_sync(FULL, hit)) return;
-    const int lane = lane_id();
-    if (filled < 32 * CELLS) {
-      const int owner = filled / CELLS, cell = filled % CELLS;
-      if (lane == owner) {
-#pragma unroll
-        for (int c = 0; c < CELLS; ++c) {
-          if (c == cell) {
-            key[c] = s;
-            w[c] = a;
-          }
-        }
-      }
-      ++filled;
-      return;
-    }
-    // full: evict the least (weight, cell, lane).  Weights are positive, so their
-    // bit patterns order like the values.
-    uint32_t lw = __float_as_uint(w[0]);
-    int lc = 0;
+  // Weights are positive, so their bit patterns order like the values.  Strict
+  // comparisons keep the smaller cell first among equal weights.
+  __device__ __forceinline__ void lane_top2() {
+    l1w = __float_as_uint(w[0]);
+    l1c = 0;
+    l2w = 0xFFFFFFFFu;
+    l2c = CELLS;  // "none": loses every tie
 #pragma unroll
     for (int c = 1; c < CELLS; ++c) {
-      const uint32_t wc = __float_as_uint(w[c]);
-      if (wc < lw) {
-        lw = wc;
-        lc = c;
-      }
+      const uint32_t x = __float_as_uint(w[c]);
+      const bool first = x < l1w, second = x < l2w;
+      l2w = first ? l1w : (second ? x : l2w);
+      l2c = first ? l1c : (second ? c : l2c);
+      l1w = first ? x : l1w;
+      l1c = first ? c : l1c;
     }
-    const uint32_t gmin = __reduce_min_sync(FULL, lw);
-    const uint32_t tie = (lw == gmin) ? static_cast<uint32_t>((lc << 5) | lane) : 0xFFFFFFFFu;
-    const uint32_t win = __reduce_min_sync(FULL, tie);
-    if (lane == static_cast<int>(win & 31u)) {
+  }
+
+  // Victim of the next eviction given every lane's smallest (weight, cell): the least
+  // (weight, cell, lane).  Two dependent redux.sync.
+  __device__ __forceinline__ void find_victim(uint32_t lw, int32_t lc, uint32_t &vmin, int32_t &vown,
+                                              int32_t &vcell) const {
+    vmin = __reduce_min_sync(FULL, lw);
+    const uint32_t t = (lw == vmin) ? static_cast<uint32_t>((lc << 5) | lane_id()) : 0xFFFFFFFFu;
+    const uint32_t win = __reduce_min_sync(FULL, t);
+    vown = static_cast<int32_t>(win & 31u);
+    vcell = static_cast<int32_t>(win >> 5);
+  }
+
+  __device__ __forceinline__ void refresh_victim() {
+    lane_top2();
+    find_victim(l1w, l1c, gmin, gown, gcell);
+  }
+
+  // slot (lane, cell) holding key s, or -1.  Warp-uniform result.
+  __device__ __forceinline__ int32_t find_slot(int32_t s) const {
+    int hit_cell = -1;
 #pragma unroll
-      for (int c = 0; c < CELLS; ++c) {
-        if (c == lc) {
-          key[c] = s;
-          w[c] = w[c] + a;
-        }
+    for (int c = 0; c < CELLS; ++c) hit_cell = (key[c] == s) ? c : hit_cell;
+    const uint32_t hs = __reduce_min_sync(
+        FULL, hit_cell >= 0 ? static_cast<uint32_t>(lane_id() * CELLS + hit_cell) : 0xFFFFFFFFu);
+    return static_cast<int32_t>(hs);
+  }
+
+  __device__ __forceinline__ void add_weight(int32_t slot, float a) {
+    const int hl = slot / CELLS, hc = slot % CELLS;
+    const bool me = lane_id() == hl;
+#pragma unroll
+    for (int c = 0; c < CELLS; ++c) w[c] = (me & (c == hc)) ? w[c] + a : w[c];
+  }
+
+  __device__ __forceinline__ void put(int32_t slot, int32_t s, float wv) {
+    const int ol = slot / CELLS, oc = slot % CELLS;
+    const bool me = lane_id() == ol;
+#pragma unroll
+    for (int c = 0; c < CELLS; ++c) {
+      const bool p = me & (c == oc);
+      w[c] = p ? wv : w[c];
+      key[c] = p ? s : key[c];
+    }
+  }
+
+  // one stream element while the sketch still has empty slots
+  __device__ __forceinline__ void add_filling(int32_t s, float a) {
+    const int32_t slot = find_slot(s);
+    if (slot >= 0) {
+      add_weight(slot, a);
+      return;
+    }
+    put(filled, s, a);
+    ++filled;
+    if (filled == 32 * CELLS) refresh_victim();
+  }
+
+  // One stream element with the sketch full.  Only the victim's lane can change its
+  // smallest weight on a miss, and its new smallest is either the re-inserted slot or
+  // its cached second smallest: the speculative victim search therefore starts after one
+  // add, one compare and one select, and the bookkeeping of the lane's own top-2 runs
+  // beside the reductions instead of in front of them.  Written with selects only: a
+  // lane-divergent branch here costs more than the rest of the step.
+  __device__ __forceinline__ void add_full(int32_t s, float a) {
+    const int lane = lane_id();
+    const bool own = lane == gown;
+    const float wnew = __uint_as_float(gmin) + a;
+    const uint32_t nb = __float_as_uint(wnew);
+    const int32_t slot = find_slot(s);
+    // speculation: this element misses and replaces the cached victim
+    const bool new_first = (nb < l2w) | ((nb == l2w) & (gcell < l2c));
+    const uint32_t sw = own ? (new_first ? nb : l2w) : l1w;
+    const int32_t sc = own ? (new_first ? gcell : l2c) : l1c;
+    uint32_t smin;
+    int32_t sown, scell;
+    find_victim(sw, sc, smin, sown, scell);
+    if (slot < 0) {  // miss (warp-uniform): commit
+      const int32_t gslot = gown * CELLS + gcell;
+      put(gslot, s, wnew);
+      if (CELLS <= 2) {  // the lane's pair, reordered
+        l2w = own ? (new_first ? l2w : nb) : l2w;
+        l2c = own ? (new_first ? l2c : gcell) : l2c;
+        l1w = sw;
+        l1c = sc;
+      } else {
+        lane_top2();
       }
+      gmin = smin;
+      gown = sown;
+      gcell = scell;
+    } else {  // hit: the speculation is void
+      add_weight(slot, a);
+      lane_top2();
+      if (slot / CELLS == gown) find_victim(l1w, l1c, gmin, gown, gcell);
     }
   }
 
@@ -173,66 +265,295 @@ struct Sketch {
   }
 };
 
+// Producer side of one row: walks the row's column groups 32 at a time (one per lane)
+// and writes the stream, in order and without the row itself, into the warp's ring.
+template <int RING>
+struct Producer {
+  const SketchArgs &a;
+  int32_t r, rb, re, rs;
+  int32_t pb;         // CSR position of lane 0's column in the current window
+  int32_t gst, glen;  // this lane's group: first entry, length (0 when it has no candidates)
+  int32_t grank;      // index of row r inside the group
+  int32_t done;       // stream entries of this lane's group already produced
+  int2 nsg;           // next window, requested one window ahead
+  int32_t nrank;
+
+  __device__ __forceinline__ Producer(const SketchArgs &args) : a(args) {}
+
+  __device__ __forceinline__ void load_next(int32_t p) {
+    nsg = make_int2(0, 0);
+    nrank = 0;
+    if (p < re) {
+      nsg = a.seg[p];
+      nrank = a.seg_rank[p];
+    }
+  }
+  __device__ __forceinline__ void take_window() {
+    gst = nsg.x;
+    glen = nsg.y >= 2 ? nsg.y : 0;
+    grank = nrank;
+    done = 0;
+  }
+  __device__ __forceinline__ void begin(int32_t row, int32_t row_begin, int32_t row_end) {
+    r = row;
+    rb = row_begin;
+    re = row_end;
+    rs = re - rb;
+    pb = rb;
+    load_next(pb + lane_id());
+    take_window();
+    load_next(pb + 32 + lane_id());
+  }
+
+  // entry q of this lane's group with the row itself skipped -> (row, alpha)
+  __device__ __forceinline__ void emit(int32_t q, int32_t *ring_s, float *ring_a, int32_t at) const {
+    const int2 e = a.cand[gst + q + (q >= grank ? 1 : 0)];
+    ring_s[at] = e.x;
+    ring_a[at] = 2.0f / static_cast<float>(rs + e.y);
+  }
+
+  // Fills the ring with up to RING elements; returns how many.  0 = stream finished.
+  __device__ __forceinline__ int produce(int32_t *ring_s, float *ring_a) {
+    const int lane = lane_id();
+    int fill = 0;
+    for (;;) {
+      const int32_t rem = glen > 0 ? glen - 1 - done : 0;
+      const unsigned pending = __ballot_sync(FULL, rem > 0);
+      if (pending == 0u) {  // window exhausted: next 32 columns
+        pb += 32;
+        if (pb >= re) break;
+        take_window();
+        load_next(pb + 32 + lane);
+        continue;
+      }
+      if (fill >= RING) break;
+      const unsigned longs = __ballot_sync(FULL, rem >= S_LONG);
+      const int first = __ffs(pending) - 1;
+      if ((longs >> first) & 1u) {
+        // the next group in stream order is a long one: whole warp, coalesced
+        const int32_t g_st = __shfl_sync(FULL, gst, first);
+        const int32_t g_rank = __shfl_sync(FULL, grank, first);
+        const int32_t g_done = __shfl_sync(FULL, done, first);
+        const int32_t g_rem = __shfl_sync(FULL, rem, first);
+        const int32_t take = g_rem < RING - fill ? g_rem : RING - fill;
+        for (int32_t i0 = 0; i0 < take; i0 += 128) {
+          int2 e[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int32_t q = g_done + i0 + u * 32 + lane;
+            if (i0 + u * 32 + lane < take) e[u] = a.cand[g_st + q + (q >= g_rank ? 1 : 0)];
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int32_t i = i0 + u * 32 + lane;
+            if (i < take) {
+              ring_s[fill + i] = e[u].x;
+              ring_a[fill + i] = 2.0f / static_cast<float>(rs + e[u].y);
+            }
+          }
+        }
+        if (lane == first) done += take;
+        fill += take;
+        continue;
+      }
+      // leading run of short groups, from `first` up to (not including) the first long
+      // group: lane-parallel, ring positions from a prefix sum
+      const unsigned later_longs = longs & ~((1u << first) - 1u);
+      const int stop = later_longs ? __ffs(later_longs) - 1 : 32;
+      const int32_t mine = (lane >= first && lane < stop) ? rem : 0;
+      int32_t incl = mine;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int32_t t = __shfl_up_sync(FULL, incl, off);
+        if (lane >= off) incl += t;
+      }
+      const int32_t space = RING - fill;
+      const int32_t before = incl - mine;
+      int32_t take = space - before;
+      take = take < 0 ? 0 : (take > mine ? mine : take);
+      {
+        // eight independent loads in flight per lane: the copy is latency bound otherwise
+        const int32_t at0 = fill + before;
+        int32_t i = 0;
+        for (; i + 8 <= take; i += 8) {
+          int2 e[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int32_t q = done + i + u;
+            e[u] = a.cand[gst + q + (q >= grank ? 1 : 0)];
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            ring_s[at0 + i + u] = e[u].x;
+            ring_a[at0 + i + u] = 2.0f / static_cast<float>(rs + e[u].y);
+          }
+        }
+        int2 e[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int32_t q = done + i + u;
+          if (i + u < take) e[u] = a.cand[gst + q + (q >= grank ? 1 : 0)];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (i + u < take) {
+            ring_s[at0 + i + u] = e[u].x;
+            ring_a[at0 + i + u] = 2.0f / static_cast<float>(rs + e[u].y);
+          }
+        }
+      }
+      done += take;
+      const int32_t total = __shfl_sync(FULL, incl, 31);
+      fill += total < space ? total : space;
+    }
+    __syncwarp();
+    return fill;
+  }
+};
+
+// Feeds `cnt` staged stream elements to the sketch.
+template <int CELLS>
+__device__ __forceinline__ void consume(Sketch<CELLS> &sk, const int32_t *bs, const float *ba,
+                                        int cnt) {
+  int t = 0;
+  for (; t < cnt && sk.filled < 32 * CELLS; ++t) sk.add_filling(bs[t], ba[t]);
+  if (t < cnt) {  // full sketch: the dependent chain, next element requested one step ahead
+    int32_t ns = bs[t];
+    float na = ba[t];
+    for (; t < cnt; ++t) {
+      const int32_t cs = ns;
+      const float cf = na;
+      const int nt = t + 1 < cnt ? t + 1 : t;
+      ns = bs[nt];
+      na = ba[nt];
+      sk.add_full(cs, cf);
+    }
+  }
+}
+
+__device__ __forceinline__ bool row_bounds_ok(const SketchArgs &a, int32_t rb, int32_t re) {
+  if (rb < 0 || re < rb || re > a.nnz) {  // malformed row pointers: flag and skip
+    if (lane_id() == 0) atomicExch(&a.ctrl[CTRL_BAD_INPUT], 1u);
+    return false;
+  }
+  return true;
+}
+
+// All rows below the heavy threshold: one warp per row, producing and consuming in turn.
 template <int CELLS>
 __global__ void __launch_bounds__(S_THREADS) sketch_kernel(SketchArgs a) {
-  const int lane = lane_id();
+  __shared__ int32_t ring_s[S_WARPS][S_RING];
+  __shared__ float ring_a[S_WARPS][S_RING];
+  const int lane = lane_id(), warp = threadIdx.x >> 5;
   const uint32_t listed = a.ctrl[CTRL_ROWS_LISTED];
+  int32_t *bs = ring_s[warp];
+  float *ba = ring_a[warp];
   Sketch<CELLS> sk;
+  Producer<S_RING> prod(a);
   for (;;) {
     uint32_t item = 0;
-    if (lane == 0) item = atomicAdd(&a.ctrl[CTRL_ROW_TICKET], 1u);
+    if (lane == 0) item = atomicAdd(&a.ctrl[CTRL_ROW_TICKET], 1u);  // starts after the heavy rows
     item = __shfl_sync(FULL, item, 0);
     if (item >= listed) break;
     const int32_t r = a.row_list[item];
     const int32_t rb = a.ptr[r], re = a.ptr[r + 1];
-    const int32_t rs = re - rb;
-    if (rb < 0 || rs < 0 || re > a.nnz) {  // malformed row pointers: flag and skip
-      if (lane == 0) atomicExch(&a.ctrl[CTRL_BAD_INPUT], 1u);
-      continue;
-    }
+    if (!row_bounds_ok(a, rb, re)) continue;
     sk.clear();
-    for (int32_t pb = rb; pb < re; pb += 32) {
-      const int32_t p = pb + lane;
-      int2 sg = make_int2(0, 0);
-      if (p < re) sg = a.seg[p];
-      unsigned act = __ballot_sync(FULL, sg.y >= 2);
-      while (act) {
-        const int j = __ffs(act) - 1;
-        act &= act - 1;
-        const int32_t st = __shfl_sync(FULL, sg.x, j);
-        const int32_t len = __shfl_sync(FULL, sg.y, j);
-        for (int32_t base = 0; base < len; base += 32) {
-          const int32_t i = base + lane;
-          int32_t s = -1;
-          float al = 0.0f;
-          if (i < len) {
-            const int2 c = a.cand[st + i];
-            if (c.x != r) {
-              s = c.x;
-              al = 2.0f / static_cast<float>(rs + c.y);
-            }
-          }
-          unsigned todo = __ballot_sync(FULL, s >= 0);
-          while (todo) {
-            const int t = __ffs(todo) - 1;
-            todo &= todo - 1;
-            sk.add(__shfl_sync(FULL, s, t), __shfl_sync(FULL, al, t));
-          }
-        }
-      }
+    prod.begin(r, rb, re);
+    for (;;) {
+      const int cnt = prod.produce(bs, ba);
+      if (cnt == 0) break;
+      consume<CELLS>(sk, bs, ba, cnt);
+      __syncwarp();
     }
     sk.select_top_k(a.k, a.table + static_cast<size_t>(r) * a.k, a.row_base);
   }
 }
 
+// barrier of one producer/consumer pair (64 threads); ids 1 and 2
+__device__ __forceinline__ void pair_barrier(int pair) {
+  asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory");
+}
+
+// Consumer and producer of one heavy row.  Each is compiled as a function of its own, with
+// its state created inside it, so the consumer's dependent chain is scheduled and
+// register-allocated as if it were alone in the kernel.
 template <int CELLS>
-bool launch_one(Context &ctx, const SketchArgs &a) {
+__device__ __noinline__ void heavy_consumer(const SketchArgs &a, const int32_t *ring_s,
+                                            const float *ring_a, int pair, int32_t r,
+                                            uint32_t total) {
+  Sketch<CELLS> sk;
+  sk.clear();
+  const uint32_t buffers = (total + H_RING - 1) / H_RING;
+  for (uint32_t b = 0; b < buffers; ++b) {
+    pair_barrier(pair);  // buffer b is ready
+    const uint32_t left = total - b * H_RING;
+    consume<CELLS>(sk, ring_s + (b & 1) * H_RING, ring_a + (b & 1) * H_RING,
+                   static_cast<int>(left < H_RING ? left : H_RING));
+  }
+  sk.select_top_k(a.k, a.table + static_cast<size_t>(r) * a.k, a.row_base);
+}
+
+__device__ __noinline__ void heavy_producer(const SketchArgs &a, int32_t *ring_s, float *ring_a,
+                                            int pair, int32_t r, int32_t rb, int32_t re,
+                                            uint32_t total) {
+  Producer<H_RING> prod(a);
+  prod.begin(r, rb, re);
+  const uint32_t buffers = (total + H_RING - 1) / H_RING;
+  for (uint32_t b = 0; b < buffers; ++b) {
+    prod.produce(ring_s + (b & 1) * H_RING, ring_a + (b & 1) * H_RING);
+    pair_barrier(pair);  // hand over buffer b; buffer b-1 has been consumed
+  }
+}
+
+// The heaviest rows: two (producer warp, consumer warp) pairs per block, one block per SM.
+// Both warps of a pair derive the number of buffers from row_work, so they meet at the
+// pair barrier the same number of times; neither waits on anything else.
+template <int CELLS>
+__global__ void __launch_bounds__(S_THREADS, 1) sketch_heavy_kernel(SketchArgs a) {
+  extern __shared__ __align__(16) unsigned char heavy_smem[];
+  __shared__ uint32_t pair_item[2];
+  const int lane = lane_id(), warp = threadIdx.x >> 5;
+  const int pair = warp >> 1;
+  const bool consumer = (warp & 1) == 0;
+  int32_t *ring_s = reinterpret_cast<int32_t *>(heavy_smem) + pair * (4 * H_RING);
+  float *ring_a = reinterpret_cast<float *>(ring_s + 2 * H_RING);
+  const uint32_t heavy = a.ctrl[CTRL_HEAVY_ROWS];
+  for (;;) {
+    if (consumer && lane == 0) pair_item[pair] = atomicAdd(&a.ctrl[CTRL_HEAVY_TICKET], 1u);
+    pair_barrier(pair);
+    const uint32_t item = pair_item[pair];
+    pair_barrier(pair);  // both have read the ticket before the next one is written
+    if (item >= heavy) break;
+    const int32_t r = a.row_list[item];
+    const int32_t rb = a.ptr[r], re = a.ptr[r + 1];
+    if (!row_bounds_ok(a, rb, re)) continue;
+    const uint32_t total = a.row_work[r];
+    if (consumer)
+      heavy_consumer<CELLS>(a, ring_s, ring_a, pair, r, total);
+    else
+      heavy_producer(a, ring_s, ring_a, pair, r, rb, re, total);
+  }
+}
+
+template <int CELLS>
+bool launch_cells(Context &ctx, const SketchArgs &a) {
+  // heavy rows on the context's stream, the rest beside them on the helper stream
+  CSG_CUDA(cudaEventRecord(ctx.ev[5], ctx.stream));
+  CSG_CUDA(cudaStreamWaitEvent(ctx.aux_stream, ctx.ev[5], 0));
+  const int heavy_smem = ctx.smem_optin - 1024;  // the whole SM: nothing else is placed there
+  CSG_CUDA(cudaFuncSetAttribute(sketch_heavy_kernel<CELLS>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, heavy_smem));
+  sketch_heavy_kernel<CELLS><<<ctx.num_sms, S_THREADS, heavy_smem, ctx.stream>>>(a);
+  CSG_CUDA(cudaGetLastError());
   int per_sm = 0;
   CSG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sketch_kernel<CELLS>, S_THREADS, 0));
   if (per_sm < 1) per_sm = 1;
-  sketch_kernel<CELLS><<<ctx.num_sms * per_sm, S_THREADS, 0, ctx.stream>>>(a);
+  sketch_kernel<CELLS><<<ctx.num_sms * per_sm, S_THREADS, 0, ctx.aux_stream>>>(a);
   CSG_CUDA(cudaGetLastError());
-  count_launches(1);
+  CSG_CUDA(cudaEventRecord(ctx.ev[6], ctx.aux_stream));
+  CSG_CUDA(cudaStreamWaitEvent(ctx.stream, ctx.ev[6], 0));
+  count_launches(2);
   return true;
 }
 
@@ -245,10 +566,13 @@ bool launch_sketch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, con
   a.nnz = nnz;
   a.k = p.k;
   a.row_base = row_base;
+  a.chunk = p.chunk;
   a.ptr = d_ptr;
   a.seg = s.seg;
+  a.seg_rank = s.seg_rank;
   a.cand = s.cand;
   a.row_list = s.row_list;
+  a.row_work = s.row_work;
   a.ctrl = s.ctrl;
   a.table = s.table;
   // rows without candidates are never visited: their entries must read as empty
@@ -256,7 +580,7 @@ bool launch_sketch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, con
   switch (p.M / 32) {
 #define CSG_CASE(C) \
   case C:           \
-    return launch_one<C>(ctx, a);
+    return launch_cells<C>(ctx, a);
     CSG_CASE(1) CSG_CASE(2) CSG_CASE(3) CSG_CASE(4) CSG_CASE(5) CSG_CASE(6) CSG_CASE(7) CSG_CASE(8)
     CSG_CASE(9) CSG_CASE(10) CSG_CASE(11) CSG_CASE(12) CSG_CASE(13) CSG_CASE(14) CSG_CASE(15)
     CSG_CASE(16)

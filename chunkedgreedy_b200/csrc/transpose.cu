@@ -4,14 +4,20 @@
 // (sporder/src/common/csr2csc.cu:38-115) and then, per row, scans whole column
 // lists to pick out the rows of the row's own chunk
 // (sporder/src/common/chunk_similarity_top_k.cu:52-84).  Candidates never leave
-// the chunk, so this library transposes every chunk on its own: one thread block
-// sorts the chunk's (column, position) pairs by column (stable LSD radix sort, in
-// shared memory when the chunk fits, in global ping-pong buffers otherwise),
-// finds the column groups and emits
+// the chunk, so this library transposes every chunk on its own: the chunk's
+// (column, position) pairs are sorted by column with a stable LSD radix sort,
+// column groups are found, and the kernels emit
 //   cand[]  : the chunk's rows grouped by column, rows ascending inside a group,
 //             each with its row length (what the Dice term needs);
-//   seg[p]  : for nonzero p (CSR order) the group of its column: (first, length);
+//   seg[p]  : for nonzero p (CSR order) the group of its column: (first, length),
+//             and seg_rank[p], the place of p's own row inside that group;
 //   row_work: per row, how many candidates its stream will hold.
+// Chunks of up to T_LS nonzeros are handled start to finish by one thread block in
+// shared memory (one read of the CSR slice, no intermediate traffic).  Heavier
+// chunks - on power-law inputs a handful of chunks hold millions of nonzeros, and
+// the rows with the longest streams live in exactly those - are cut into tiles and
+// sorted by the whole grid: per pass a tile histogram, a per-chunk scan and a
+// stable tile scatter, then a group search per element.
 // A caller-promised symmetric pattern needs no separate path: the transpose of a
 // symmetric pattern restricted to the chunk is what the reference reads from the
 // aliased CSR arrays (sporder/src/common/csr2csc.h:52-54).
@@ -33,9 +39,34 @@ struct TransposeArgs {
   const int32_t *ptr, *ind;
   uint32_t *keyA, *keyB, *payA, *payB;
   int2 *cand, *seg;
+  int32_t *seg_rank;
   uint32_t *row_work;
   uint32_t *ctrl;
+  // heavy chunks (more than T_LS nonzeros)
+  int32_t *heavy_chunk;      // chunk ids, in arrival order
+  int32_t *heavy_tile_base;  // first tile of each heavy chunk, plus the total
+  uint32_t *tile_hist;       // [tile][256] digit counts, then offsets
+  uint32_t *digit_base;      // [heavy chunk][256]
 };
+
+struct ChunkSpan {
+  int32_t cs, rows, b, L;
+};
+
+__device__ __forceinline__ ChunkSpan chunk_span(const TransposeArgs &a, int32_t q) {
+  ChunkSpan c;
+  const int64_t cs64 = static_cast<int64_t>(q) * a.chunk;
+  c.cs = static_cast<int32_t>(cs64);
+  const int32_t ce = (cs64 + a.chunk > a.n) ? a.n : static_cast<int32_t>(cs64 + a.chunk);
+  c.rows = ce - c.cs;
+  c.b = a.ptr[c.cs];
+  c.L = a.ptr[ce] - c.b;
+  if (c.b < 0 || c.L < 0 || c.L > a.nnz - c.b) {  // malformed row pointers: flag and skip
+    atomicExch(&a.ctrl[CTRL_BAD_INPUT], 1u);
+    c.L = 0;
+  }
+  return c;
+}
 
 struct Shared {
   uint32_t wc[T_WARPS * 256];
@@ -44,7 +75,6 @@ struct Shared {
   int32_t warp_last[T_WARPS];
   int32_t carry;
   int32_t ticket;
-  uint32_t bucket[33];
   int32_t sptr[T_RP + 1];
   uint32_t row_work[T_RP];
   uint32_t skey[2][T_LS];
@@ -217,6 +247,7 @@ __device__ void emit_groups(const uint32_t *K, const PayT *P, uint32_t *S, PayT 
                                     : (a.ptr[row + 1] - a.ptr[row]);
     a.cand[b + i] = make_int2(row, rl);
     a.seg[b + p] = make_int2(b + st, len);
+    a.seg_rank[b + p] = i - st;
     if (len >= 2) {
       if (rows_in_smem)
         atomicAdd(&sh.row_work[row - cs], static_cast<uint32_t>(len - 1));
@@ -230,68 +261,279 @@ __global__ void __launch_bounds__(T_THREADS, 1) transpose_kernel(TransposeArgs a
   extern __shared__ __align__(16) unsigned char smem_raw[];
   Shared &sh = *reinterpret_cast<Shared *>(smem_raw);
   const int tid = threadIdx.x;
-  if (tid < 33) sh.bucket[tid] = 0;
   for (;;) {
     __syncthreads();
     if (tid == 0) sh.ticket = static_cast<int32_t>(atomicAdd(&a.ctrl[CTRL_CHUNK_TICKET], 1u));
     __syncthreads();
     const int32_t q = sh.ticket;
     if (q >= a.num_chunks) break;
-    const int64_t cs64 = static_cast<int64_t>(q) * a.chunk;
-    const int32_t cs = static_cast<int32_t>(cs64);
-    const int32_t ce = (cs64 + a.chunk > a.n) ? a.n : static_cast<int32_t>(cs64 + a.chunk);
-    const int32_t rows = ce - cs;
-    const int32_t b = a.ptr[cs];
-    int L = a.ptr[ce] - b;
-    if (b < 0 || L < 0 || L > a.nnz - b) {  // malformed row pointers: flag and skip
-      if (tid == 0) atomicExch(&a.ctrl[CTRL_BAD_INPUT], 1u);
-      L = 0;
-    }
+    const ChunkSpan c = chunk_span(a, q);
+    const int32_t cs = c.cs, rows = c.rows, b = c.b;
+    const int L = c.L;
+    if (L > T_LS || L == 0) continue;  // heavy chunks go through the tiled kernels
     const bool rows_in_smem = rows <= T_RP;
     if (rows_in_smem) {
       for (int i = tid; i <= rows; i += T_THREADS) sh.sptr[i] = a.ptr[cs + i];
       for (int i = tid; i < rows; i += T_THREADS) sh.row_work[i] = 0;
     }
     __syncthreads();
-    if (L > 0) {
-      const uint32_t *kin0 = reinterpret_cast<const uint32_t *>(a.ind + b);
-      const int P = a.passes;
-      if (L <= T_LS) {
-        radix_pass<uint16_t, true>(kin0, nullptr, sh.skey[0], sh.spay[0], L, 0, sh);
-        for (int ps = 1; ps < P; ++ps)
-          radix_pass<uint16_t, false>(sh.skey[(ps - 1) & 1], sh.spay[(ps - 1) & 1], sh.skey[ps & 1],
-                                      sh.spay[ps & 1], L, 8 * ps, sh);
-        const int f = (P - 1) & 1;
-        emit_groups<uint16_t>(sh.skey[f], sh.spay[f], sh.skey[f ^ 1], sh.spay[f ^ 1], L, b, cs, rows,
-                              rows_in_smem, a, sh);
-      } else {
-        uint32_t *kb[2] = {a.keyA + b, a.keyB + b};
-        uint32_t *pb[2] = {a.payA + b, a.payB + b};
-        radix_pass<uint32_t, true>(kin0, nullptr, kb[0], pb[0], L, 0, sh);
-        for (int ps = 1; ps < P; ++ps)
-          radix_pass<uint32_t, false>(kb[(ps - 1) & 1], pb[(ps - 1) & 1], kb[ps & 1], pb[ps & 1], L,
-                                      8 * ps, sh);
-        const int f = (P - 1) & 1;
-        emit_groups<uint32_t>(kb[f], pb[f], kb[f ^ 1], pb[f ^ 1], L, b, cs, rows, rows_in_smem, a,
-                              sh);
+    const uint32_t *kin0 = reinterpret_cast<const uint32_t *>(a.ind + b);
+    const int P = a.passes;
+    radix_pass<uint16_t, true>(kin0, nullptr, sh.skey[0], sh.spay[0], L, 0, sh);
+    for (int ps = 1; ps < P; ++ps)
+      radix_pass<uint16_t, false>(sh.skey[(ps - 1) & 1], sh.spay[(ps - 1) & 1], sh.skey[ps & 1],
+                                  sh.spay[ps & 1], L, 8 * ps, sh);
+    const int f = (P - 1) & 1;
+    emit_groups<uint16_t>(sh.skey[f], sh.spay[f], sh.skey[f ^ 1], sh.spay[f ^ 1], L, b, cs, rows,
+                          rows_in_smem, a, sh);
+    __syncthreads();
+    if (rows_in_smem)
+      for (int i = tid; i < rows; i += T_THREADS) a.row_work[cs + i] = sh.row_work[i];
+  }
+}
+
+// ---- heavy chunks: tiled, whole-grid sort ----------------------------------------
+
+__global__ void classify_chunks_kernel(TransposeArgs a) {
+  for (int32_t q = blockIdx.x * blockDim.x + threadIdx.x; q < a.num_chunks;
+       q += gridDim.x * blockDim.x) {
+    const ChunkSpan c = chunk_span(a, q);
+    if (c.L > T_LS) a.heavy_chunk[atomicAdd(&a.ctrl[CTRL_HEAVY_COUNT], 1u)] = q;
+  }
+}
+
+// exclusive scan of the heavy chunks' tile counts (one block)
+__global__ void __launch_bounds__(1024) heavy_tiles_kernel(TransposeArgs a) {
+  __shared__ int32_t sm[32];
+  __shared__ int32_t carry_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int32_t H = static_cast<int32_t>(a.ctrl[CTRL_HEAVY_COUNT]);
+  if (threadIdx.x == 0) carry_s = 0;
+  __syncthreads();
+  for (int32_t base = 0; base < H; base += 1024) {
+    const int32_t i = base + threadIdx.x;
+    int32_t v = 0;
+    if (i < H) v = (chunk_span(a, a.heavy_chunk[i]).L + T_TILE - 1) / T_TILE;
+    int32_t incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int32_t t = __shfl_up_sync(FULL, incl, off);
+      if (lane >= off) incl += t;
+    }
+    if (lane == 31) sm[warp] = incl;
+    __syncthreads();
+    int32_t wbase = 0, tot = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int32_t t = sm[w];
+      if (w < warp) wbase += t;
+      tot += t;
+    }
+    const int32_t carry = carry_s;
+    if (i < H) a.heavy_tile_base[i] = carry + wbase + incl - v;
+    __syncthreads();
+    if (threadIdx.x == 0) carry_s = carry + tot;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    a.heavy_tile_base[H] = carry_s;
+    a.ctrl[CTRL_HEAVY_TILES] = static_cast<uint32_t>(carry_s);
+  }
+}
+
+struct TileRef {
+  int32_t h, b, L, off, cnt, cs, rows;
+};
+
+// tile t -> its heavy chunk and range (uniform over the block)
+__device__ __forceinline__ TileRef tile_ref(const TransposeArgs &a, int32_t t, int32_t H) {
+  int32_t lo = 0, hi = H;  // heavy_tile_base[lo] <= t < heavy_tile_base[hi]
+  while (hi - lo > 1) {
+    const int32_t mid = (lo + hi) >> 1;
+    if (a.heavy_tile_base[mid] <= t)
+      lo = mid;
+    else
+      hi = mid;
+  }
+  const ChunkSpan c = chunk_span(a, a.heavy_chunk[lo]);
+  TileRef r;
+  r.h = lo;
+  r.b = c.b;
+  r.L = c.L;
+  r.cs = c.cs;
+  r.rows = c.rows;
+  r.off = (t - a.heavy_tile_base[lo]) * T_TILE;
+  r.cnt = c.L - r.off < T_TILE ? c.L - r.off : T_TILE;
+  return r;
+}
+
+__device__ __forceinline__ const uint32_t *pass_src_keys(const TransposeArgs &a, int ps, int32_t b) {
+  if (ps == 0) return reinterpret_cast<const uint32_t *>(a.ind + b);
+  return ((ps - 1) & 1 ? a.keyB : a.keyA) + b;
+}
+
+__global__ void __launch_bounds__(T_THREADS) heavy_hist_kernel(TransposeArgs a, int ps) {
+  __shared__ uint32_t hist[256];
+  const int32_t TT = static_cast<int32_t>(a.ctrl[CTRL_HEAVY_TILES]);
+  const int32_t H = static_cast<int32_t>(a.ctrl[CTRL_HEAVY_COUNT]);
+  const int shift = 8 * ps;
+  for (int32_t t = blockIdx.x; t < TT; t += gridDim.x) {
+    const TileRef r = tile_ref(a, t, H);
+    const uint32_t *kin = pass_src_keys(a, ps, r.b) + r.off;
+    if (threadIdx.x < 256) hist[threadIdx.x] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < r.cnt; i += T_THREADS) atomicAdd(&hist[(kin[i] >> shift) & 255u], 1u);
+    __syncthreads();
+    if (threadIdx.x < 256) a.tile_hist[static_cast<size_t>(t) * 256 + threadIdx.x] = hist[threadIdx.x];
+    __syncthreads();
+  }
+}
+
+// per heavy chunk: counts -> offsets of every (tile, digit) inside the digit's run,
+// and the start of every digit's run
+__global__ void __launch_bounds__(256) heavy_scan_kernel(TransposeArgs a) {
+  __shared__ uint32_t sm[8];
+  const int32_t H = static_cast<int32_t>(a.ctrl[CTRL_HEAVY_COUNT]);
+  const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
+  for (int32_t h = blockIdx.x; h < H; h += gridDim.x) {
+    const int32_t t0 = a.heavy_tile_base[h], t1 = a.heavy_tile_base[h + 1];
+    uint32_t run = 0;
+    for (int32_t t = t0; t < t1; ++t) {
+      uint32_t *cell = a.tile_hist + static_cast<size_t>(t) * 256 + d;
+      const uint32_t v = *cell;
+      *cell = run;
+      run += v;
+    }
+    uint32_t incl = run;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t t = __shfl_up_sync(FULL, incl, off);
+      if (lane >= off) incl += t;
+    }
+    __syncthreads();
+    if (lane == 31) sm[warp] = incl;
+    __syncthreads();
+    uint32_t wbase = 0;
+    for (int w = 0; w < warp; ++w) wbase += sm[w];
+    a.digit_base[static_cast<size_t>(h) * 256 + d] = wbase + incl - run;
+  }
+}
+
+__global__ void __launch_bounds__(T_THREADS) heavy_scatter_kernel(TransposeArgs a, int ps) {
+  __shared__ uint32_t wc[T_WARPS * 256];
+  const int32_t TT = static_cast<int32_t>(a.ctrl[CTRL_HEAVY_TILES]);
+  const int32_t H = static_cast<int32_t>(a.ctrl[CTRL_HEAVY_COUNT]);
+  const int shift = 8 * ps;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int32_t t = blockIdx.x; t < TT; t += gridDim.x) {
+    const TileRef r = tile_ref(a, t, H);
+    const uint32_t *kin = pass_src_keys(a, ps, r.b) + r.off;
+    const uint32_t *pin = ps == 0 ? nullptr : ((ps - 1) & 1 ? a.payB : a.payA) + r.b + r.off;
+    uint32_t *kout = (ps & 1 ? a.keyB : a.keyA) + r.b;
+    uint32_t *pout = (ps & 1 ? a.payB : a.payA) + r.b;
+    for (int j = tid; j < T_WARPS * 256; j += T_THREADS) wc[j] = 0;
+    __syncthreads();
+    uint32_t key[T_IPT], rk[T_IPT], pay[T_IPT];
+    const int wbase = warp * (32 * T_IPT);
+#pragma unroll
+    for (int i = 0; i < T_IPT; ++i) {
+      const int idx = wbase + i * 32 + lane;
+      const bool valid = idx < r.cnt;
+      key[i] = valid ? kin[idx] : 0u;
+      pay[i] = ps == 0 ? static_cast<uint32_t>(r.off + idx) : (valid ? pin[idx] : 0u);
+      const uint32_t d = valid ? ((key[i] >> shift) & 255u) : 256u;
+      const unsigned peers = __match_any_sync(FULL, d);
+      const int leader = __ffs(peers) - 1;
+      uint32_t pre = 0;
+      if (lane == leader && valid) {
+        pre = wc[warp * 256 + d];
+        wc[warp * 256 + d] = pre + __popc(peers);
+      }
+      pre = __shfl_sync(FULL, pre, leader);
+      rk[i] = pre + __popc(peers & ((1u << lane) - 1u));
+      __syncwarp();
+    }
+    __syncthreads();
+    if (tid < 256) {
+      uint32_t run = a.digit_base[static_cast<size_t>(r.h) * 256 + tid] +
+                     a.tile_hist[static_cast<size_t>(t) * 256 + tid];
+#pragma unroll
+      for (int w = 0; w < T_WARPS; ++w) {
+        const uint32_t v = wc[w * 256 + tid];
+        wc[w * 256 + tid] = run;
+        run += v;
       }
     }
     __syncthreads();
-    if (rows_in_smem) {
-      for (int i = tid; i < rows; i += T_THREADS) {
-        const uint32_t t = sh.row_work[i];
-        a.row_work[cs + i] = t;
-        if (t) atomicAdd(&sh.bucket[32 - __clz(t)], 1u);
-      }
-    } else {
-      for (int i = tid; i < rows; i += T_THREADS) {
-        const uint32_t t = __ldcg(&a.row_work[cs + i]);  // accumulated with global atomics
-        if (t) atomicAdd(&sh.bucket[32 - __clz(t)], 1u);
+#pragma unroll
+    for (int i = 0; i < T_IPT; ++i) {
+      const int idx = wbase + i * 32 + lane;
+      if (idx < r.cnt) {
+        const uint32_t d = (key[i] >> shift) & 255u;
+        const uint32_t dst = wc[warp * 256 + d] + rk[i];
+        kout[dst] = key[i];
+        pout[dst] = pay[i];
       }
     }
+    __syncthreads();
+  }
+}
+
+// Group of every sorted element by two bounded binary searches: a column group
+// has at most one entry per row of the chunk, so its ends lie within `rows`
+// positions of the element.
+__global__ void __launch_bounds__(T_THREADS) heavy_emit_kernel(TransposeArgs a) {
+  const int32_t TT = static_cast<int32_t>(a.ctrl[CTRL_HEAVY_TILES]);
+  const int32_t H = static_cast<int32_t>(a.ctrl[CTRL_HEAVY_COUNT]);
+  const int f = (a.passes - 1) & 1;
+  for (int32_t t = blockIdx.x; t < TT; t += gridDim.x) {
+    const TileRef r = tile_ref(a, t, H);
+    const uint32_t *K = (f ? a.keyB : a.keyA) + r.b;
+    const uint32_t *P = (f ? a.payB : a.payA) + r.b;
+    for (int li = threadIdx.x; li < r.cnt; li += T_THREADS) {
+      const int32_t i = r.off + li;
+      const uint32_t key = K[i];
+      int32_t lo = i - (r.rows - 1) < 0 ? 0 : i - (r.rows - 1), hi = i;  // first index with K >= key
+      while (lo < hi) {
+        const int32_t mid = (lo + hi) >> 1;
+        if (K[mid] < key)
+          lo = mid + 1;
+        else
+          hi = mid;
+      }
+      const int32_t st = lo;
+      lo = i + 1;
+      hi = i + r.rows < r.L ? i + r.rows : r.L;  // first index with K > key
+      while (lo < hi) {
+        const int32_t mid = (lo + hi) >> 1;
+        if (K[mid] <= key)
+          lo = mid + 1;
+        else
+          hi = mid;
+      }
+      const int32_t len = lo - st;
+      const int32_t p = static_cast<int32_t>(P[i]);
+      const int32_t row = row_of(a.ptr, r.cs, r.cs + r.rows, r.b + p);
+      a.cand[r.b + i] = make_int2(row, a.ptr[row + 1] - a.ptr[row]);
+      a.seg[r.b + p] = make_int2(r.b + st, len);
+      a.seg_rank[r.b + p] = i - st;
+      if (len >= 2) atomicAdd(&a.row_work[row], static_cast<uint32_t>(len - 1));
+    }
+  }
+}
+
+// rows per power-of-two bucket of row_work
+__global__ void __launch_bounds__(256) bucket_count_kernel(int32_t n, const uint32_t *row_work,
+                                                           uint32_t *ctrl) {
+  __shared__ uint32_t bucket[33];
+  if (threadIdx.x < 33) bucket[threadIdx.x] = 0;
+  __syncthreads();
+  for (int32_t r = blockIdx.x * blockDim.x + threadIdx.x; r < n; r += gridDim.x * blockDim.x) {
+    const uint32_t t = __ldcg(row_work + r);
+    if (t) atomicAdd(&bucket[32 - __clz(t)], 1u);
   }
   __syncthreads();
-  if (tid < 33 && sh.bucket[tid]) atomicAdd(&a.ctrl[CTRL_BUCKET_COUNT + tid], sh.bucket[tid]);
+  if (threadIdx.x < 33 && bucket[threadIdx.x])
+    atomicAdd(&ctrl[CTRL_BUCKET_COUNT + threadIdx.x], bucket[threadIdx.x]);
 }
 
 // Heaviest bucket first: rows with 2^(b-1) <= work < 2^b sit in bucket b.
@@ -304,6 +546,12 @@ __global__ void bucket_scan_kernel(uint32_t *ctrl) {
       ctrl[CTRL_BUCKET_FILL + b] = 0;
     }
     ctrl[CTRL_ROWS_LISTED] = run;
+    // rows with at least 2^(SKETCH_HEAVY_BUCKET-1) stream elements head the list; the
+    // heavy sketch kernel takes them, the other kernel's tickets start behind them
+    const uint32_t heavy = ctrl[CTRL_BUCKET_BASE + SKETCH_HEAVY_BUCKET - 1];
+    ctrl[CTRL_HEAVY_ROWS] = heavy;
+    ctrl[CTRL_HEAVY_TICKET] = 0;
+    ctrl[CTRL_ROW_TICKET] = heavy;
   }
 }
 
@@ -346,23 +594,50 @@ bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32
   a.payB = s.payB;
   a.cand = s.cand;
   a.seg = s.seg;
+  a.seg_rank = s.seg_rank;
   a.row_work = s.row_work;
   a.ctrl = s.ctrl;
+  a.heavy_chunk = s.heavy_chunk;
+  a.heavy_tile_base = s.heavy_tile_base;
+  a.tile_hist = s.tile_hist;
+  a.digit_base = s.digit_base;
   const size_t smem = sizeof(Shared);
   CSG_CUDA(cudaFuncSetAttribute(transpose_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(smem)));
-  CSG_CUDA(cudaMemsetAsync(s.ctrl, 0, sizeof(uint32_t) * CTRL_WORDS, ctx.stream));
-  CSG_CUDA(cudaMemsetAsync(s.row_work, 0, sizeof(uint32_t) * static_cast<size_t>(n), ctx.stream));
-  const int grid = a.num_chunks < ctx.num_sms ? a.num_chunks : ctx.num_sms;
-  transpose_kernel<<<grid, T_THREADS, smem, ctx.stream>>>(a);
+  cudaStream_t st = ctx.stream;
+  CSG_CUDA(cudaMemsetAsync(s.ctrl, 0, sizeof(uint32_t) * CTRL_WORDS, st));
+  CSG_CUDA(cudaMemsetAsync(s.row_work, 0, sizeof(uint32_t) * static_cast<size_t>(n), st));
+  int cgrid = (a.num_chunks + 255) / 256;
+  if (cgrid > ctx.num_sms * 4) cgrid = ctx.num_sms * 4;
+  classify_chunks_kernel<<<cgrid, 256, 0, st>>>(a);
   CSG_CUDA(cudaGetLastError());
-  bucket_scan_kernel<<<1, 32, 0, ctx.stream>>>(s.ctrl);
+  heavy_tiles_kernel<<<1, 1024, 0, st>>>(a);
+  CSG_CUDA(cudaGetLastError());
+  // heavy chunks first: the rows with the longest streams live in them
+  const int hgrid = ctx.num_sms * 2;
+  int sgrid = a.num_chunks < ctx.num_sms ? a.num_chunks : ctx.num_sms;
+  for (int ps = 0; ps < a.passes; ++ps) {
+    heavy_hist_kernel<<<hgrid, T_THREADS, 0, st>>>(a, ps);
+    CSG_CUDA(cudaGetLastError());
+    heavy_scan_kernel<<<sgrid, 256, 0, st>>>(a);
+    CSG_CUDA(cudaGetLastError());
+    heavy_scatter_kernel<<<hgrid, T_THREADS, 0, st>>>(a, ps);
+    CSG_CUDA(cudaGetLastError());
+  }
+  heavy_emit_kernel<<<hgrid * 2, T_THREADS, 0, st>>>(a);
+  CSG_CUDA(cudaGetLastError());
+  const int grid = a.num_chunks < ctx.num_sms ? a.num_chunks : ctx.num_sms;
+  transpose_kernel<<<grid, T_THREADS, smem, st>>>(a);
   CSG_CUDA(cudaGetLastError());
   int lgrid = (n + 255) / 256;
   if (lgrid > ctx.num_sms * 8) lgrid = ctx.num_sms * 8;
-  row_list_kernel<<<lgrid, 256, 0, ctx.stream>>>(n, s.row_work, s.ctrl, s.row_list);
+  bucket_count_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl);
   CSG_CUDA(cudaGetLastError());
-  count_launches(3);
+  bucket_scan_kernel<<<1, 32, 0, st>>>(s.ctrl);
+  CSG_CUDA(cudaGetLastError());
+  row_list_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl, s.row_list);
+  CSG_CUDA(cudaGetLastError());
+  count_launches(7 + 3 * a.passes);
   return true;
 }
 

@@ -216,3 +216,33 @@ def test_native_library_is_the_one_that_ran():
     assert sp.kernel_launches() >= before + 5
     maps = open("/proc/self/maps").read()
     assert "libsporder_b200.so" in maps
+
+
+def test_gcn_gradients_match_dense_reference_and_reordering_is_equivalent():
+    # the SpMM autograd function against a dense torch fp32 reference of the same op,
+    # and training on P A P^T with permuted features gives the same losses
+    sp = _sp()
+    from chunkedgreedy_b200 import gcn
+    ptr, ind, val, sym, params = cases.build("rmat11gcn")
+    n = ptr.size - 1
+    dp, di, dv = _dev(ptr), _dev(ind), _dev(val)
+    dense = torch.zeros((n, n), device="cuda")
+    rows = torch.repeat_interleave(torch.arange(n, device="cuda"), (dp[1:] - dp[:-1]).long())
+    dense[rows, di.long()] = dv
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn((n, 32), device="cuda", generator=g, requires_grad=True)
+    op = gcn.GraphOperator(dp, di, dv)
+    y = gcn.SpMMFn.apply(x, op)
+    y.square().sum().backward()
+    xr = x.detach().clone().requires_grad_(True)
+    yr = dense @ xr
+    yr.square().sum().backward()
+    assert torch.allclose(y, yr, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(x.grad, xr.grad, rtol=1e-4, atol=1e-4)
+    feats = torch.randn((n, 16), device="cuda", generator=g)
+    labels = torch.randint(0, 4, (n,), device="cuda", generator=g)
+    res = gcn.reorder_and_train(dp, di, dv, feats, labels, hidden=16, classes=4, epochs=5,
+                                warmup=0)
+    a, b = res["original"]["final_loss"], res["reordered"]["final_loss"]
+    assert abs(a - b) <= 1e-3 * max(1.0, abs(a))
+    assert sorted(res["order"].cpu().tolist()) == list(range(n))
