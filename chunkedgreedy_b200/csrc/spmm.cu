@@ -8,11 +8,13 @@
 // many row gathers in flight.
 //
 // Row tiling: a group of G = w/VEC lanes (VEC = 4 floats where w allows) owns one
-// row piece and walks its nonzeros; every lane of the group loads its VEC columns
-// of B[col] (one coalesced segment per group) and accumulates in registers.  A
-// warp therefore handles 32/G row pieces at once.  Rows longer than SPLIT are cut
-// into pieces that are added with atomics (C is zeroed first for those rows), so a
-// hub row never serialises on one warp.
+// row piece and walks its nonzeros four at a time; every lane of the group loads its
+// VEC columns of B[col] (one coalesced segment per group) and accumulates in
+// registers.  A warp therefore handles 32/G rows at once, and each group fetches its
+// next row from a ticket counter the moment it is done, so uneven row lengths do not
+// idle lanes.  Rows longer than SPLIT are cut into pieces that all groups share and
+// that are added with atomics (C is zeroed first for those rows), so a hub row never
+// serialises on one warp.
 #include <mutex>
 
 #include "../../include/sporder_b200.h"
@@ -48,85 +50,146 @@ struct SpmmArgs {
   const float *val;
   const float *B;
   float *C;
-  int32_t *long_rows;     // rows longer than SPLIT, appended by the first launch
-  uint32_t *long_count;
+  // scratch: [0] row ticket, [2..3] packed (long rows, pieces) counter, then the queue
+  uint32_t *ctrl;
+  int2 *long_rows;  // (row, first piece number), in piece order
 };
 
-// One row piece [pb, pe) of `row` for the lane group: G lanes, VEC columns each,
-// one column panel of G*VEC at a time when w is wider.
+constexpr int CTRL_TICKET = 0;
+constexpr int CTRL_PACKED = 2;  // 64-bit: high word = long rows queued, low word = pieces so far
+constexpr int CTRL_SCRATCH_WORDS = 64;
+
+// FMA of up to four nonzeros [p, p + cnt) of one row into acc, loads issued together.
 template <int G, int VEC>
-__device__ __forceinline__ void row_piece(const SpmmArgs &a, int32_t row, int32_t pb, int32_t pe,
-                                          int gl, bool accumulate) {
-  const int panels = a.w / (G * VEC);
-  for (int panel = 0; panel < panels; ++panel) {
-    const int32_t col0 = panel * G * VEC + gl * VEC;
-    float acc[VEC];
+__device__ __forceinline__ void fma4(const SpmmArgs &a, int32_t p, int cnt, int32_t col0,
+                                     float (&acc)[VEC]) {
+  int32_t c[4];
+  float x[4];
+  float b[4][VEC];
 #pragma unroll
-    for (int v = 0; v < VEC; ++v) acc[v] = 0.0f;
-    int32_t p = pb;
-    // four gathers in flight per lane
-    for (; p + 4 <= pe; p += 4) {
-      int32_t c[4];
-      float x[4];
-      float b[4][VEC];
+  for (int u = 0; u < 4; ++u) {
+    const bool on = u < cnt;
+    c[u] = on ? __ldg(a.ind + p + u) : 0;
+    x[u] = on ? __ldg(a.val + p + u) : 0.0f;
+  }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        c[u] = __ldg(a.ind + p + u);
-        x[u] = __ldg(a.val + p + u);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) load_b<VEC>(a.B + static_cast<size_t>(c[u]) * a.w + col0, b[u]);
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-#pragma unroll
-        for (int v = 0; v < VEC; ++v) acc[v] = fmaf(x[u], b[u][v], acc[v]);
-    }
-    for (; p < pe; ++p) {
-      const int32_t c = __ldg(a.ind + p);
-      const float x = __ldg(a.val + p);
-      float b[VEC];
-      load_b<VEC>(a.B + static_cast<size_t>(c) * a.w + col0, b);
-#pragma unroll
-      for (int v = 0; v < VEC; ++v) acc[v] = fmaf(x, b[v], acc[v]);
-    }
-    float *out = a.C + static_cast<size_t>(row) * a.w + col0;
-    if (accumulate) {
-#pragma unroll
-      for (int v = 0; v < VEC; ++v) atomicAdd(out + v, acc[v]);
-    } else if (VEC == 4) {
-      *reinterpret_cast<float4 *>(out) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    } else if (VEC == 2) {
-      *reinterpret_cast<float2 *>(out) = make_float2(acc[0], acc[1]);
+  for (int u = 0; u < 4; ++u) {
+    if (u < cnt) {
+      load_b<VEC>(a.B + static_cast<size_t>(c[u]) * a.w + col0, b[u]);
     } else {
-      out[0] = acc[0];
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) b[u][v] = 0.0f;
     }
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc[v] = fmaf(x[u], b[u][v], acc[v]);
+}
+
+template <int VEC>
+__device__ __forceinline__ void store_c(float *out, const float (&acc)[VEC], bool accumulate) {
+  if (accumulate) {
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) atomicAdd(out + v, acc[v]);
+  } else if (VEC == 4) {
+    *reinterpret_cast<float4 *>(out) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  } else if (VEC == 2) {
+    *reinterpret_cast<float2 *>(out) = make_float2(acc[0], acc[1]);
+  } else {
+    out[0] = acc[0];
   }
 }
 
-// First launch: one lane group per row.  Rows longer than SPLIT are zeroed and
-// queued instead of computed.
+// First launch.  Every lane group is persistent: it takes the next row from a ticket
+// counter as soon as its current row is finished, so the groups of a warp never wait
+// for the one with the longest row.  Rows longer than SPLIT are zeroed and queued for
+// the second launch.  (w == G * VEC here; wider matrices take the panel kernel.)
 template <int G, int VEC>
 __global__ void __launch_bounds__(M_THREADS) spmm_rows_kernel(SpmmArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int gl = lane % G;
+  const unsigned gmask = (G == 32) ? FULL : (((1u << G) - 1u) << (lane - gl));
+  const int32_t col0 = gl * VEC;
+  int32_t row = -1, p = 0, pe = 0;
+  bool done = false;
+  float acc[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) acc[v] = 0.0f;
+  for (;;) {
+    if (p >= pe && !done) {
+      if (row >= 0) store_c<VEC>(a.C + static_cast<size_t>(row) * a.w + col0, acc, false);
+      int32_t r = 0;
+      if (gl == 0) r = static_cast<int32_t>(atomicAdd(&a.ctrl[CTRL_TICKET], 1u));
+      r = __shfl_sync(gmask, r, lane - gl);
+      row = -1;
+      if (r >= a.n) {
+        done = true;
+      } else {
+        const int32_t b = a.ptr[r], e = a.ptr[r + 1];
+        if (e - b > SPLIT) {
+          for (int32_t j = gl * VEC; j < a.w; j += G * VEC)
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) a.C[static_cast<size_t>(r) * a.w + j + v] = 0.0f;
+          if (gl == 0) {
+            const unsigned long long pieces = static_cast<unsigned long long>((e - b + SPLIT - 1) / SPLIT);
+            const unsigned long long old = atomicAdd(
+                reinterpret_cast<unsigned long long *>(a.ctrl + CTRL_PACKED), (1ull << 32) | pieces);
+            a.long_rows[old >> 32] = make_int2(r, static_cast<int32_t>(old & 0xFFFFFFFFu));
+          }
+        } else {
+          row = r;
+          p = b;
+          pe = e;
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) acc[v] = 0.0f;
+        }
+      }
+    }
+    if (__all_sync(FULL, done)) break;
+    const int cnt = pe - p < 4 ? pe - p : 4;
+    if (cnt > 0) fma4<G, VEC>(a, p, cnt, col0, acc);
+    p += cnt;
+  }
+}
+
+// Matrices wider than one panel of G*VEC columns: one lane group per row and panel loop.
+template <int G, int VEC>
+__global__ void __launch_bounds__(M_THREADS) spmm_panel_kernel(SpmmArgs a) {
   constexpr int PER_WARP = 32 / G;
   const int lane = threadIdx.x & 31;
   const int sub = lane / G, gl = lane % G;
   const int32_t warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int32_t warps = (gridDim.x * blockDim.x) >> 5;
+  const int panels = a.w / (G * VEC);
   for (int32_t base = warp_global * PER_WARP; base < a.n; base += warps * PER_WARP) {
     const int32_t row = base + sub;
     if (row >= a.n) continue;
     const int32_t pb = a.ptr[row], pe = a.ptr[row + 1];
     if (pe - pb > SPLIT) {
       for (int32_t j = gl; j < a.w; j += G) a.C[static_cast<size_t>(row) * a.w + j] = 0.0f;
-      if (gl == 0) a.long_rows[atomicAdd(a.long_count, 1u)] = row;
+      if (gl == 0) {
+        const unsigned long long pieces = static_cast<unsigned long long>((pe - pb + SPLIT - 1) / SPLIT);
+        const unsigned long long old = atomicAdd(
+            reinterpret_cast<unsigned long long *>(a.ctrl + CTRL_PACKED), (1ull << 32) | pieces);
+        a.long_rows[old >> 32] = make_int2(row, static_cast<int32_t>(old & 0xFFFFFFFFu));
+      }
       continue;
     }
-    row_piece<G, VEC>(a, row, pb, pe, gl, false);
+    for (int panel = 0; panel < panels; ++panel) {
+      const int32_t col0 = panel * G * VEC + gl * VEC;
+      float acc[VEC];
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) acc[v] = 0.0f;
+      for (int32_t p = pb; p < pe; p += 4) fma4<G, VEC>(a, p, pe - p < 4 ? pe - p : 4, col0, acc);
+      store_c<VEC>(a.C + static_cast<size_t>(row) * a.w + col0, acc, false);
+    }
   }
 }
 
-// Second launch: the queued long rows, SPLIT nonzeros per lane group, added with
-// atomics.  Every group walks the (short) queue and takes the pieces that fall to it.
+// Second launch: the pieces (SPLIT nonzeros each) of the queued long rows, spread over
+// all lane groups; piece number -> queue entry by binary search on the entries' first
+// piece numbers (ascending by construction).  Partial rows are added with atomics.
 template <int G, int VEC>
 __global__ void __launch_bounds__(M_THREADS) spmm_long_kernel(SpmmArgs a) {
   constexpr int PER_WARP = 32 / G;
@@ -134,35 +197,48 @@ __global__ void __launch_bounds__(M_THREADS) spmm_long_kernel(SpmmArgs a) {
   const int sub = lane / G, gl = lane % G;
   const int32_t group = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * PER_WARP + sub;
   const int32_t groups = ((gridDim.x * blockDim.x) >> 5) * PER_WARP;
-  const uint32_t count = *a.long_count;
-  int32_t turn = 0;  // running piece number over the whole queue
-  for (uint32_t li = 0; li < count; ++li) {
-    const int32_t row = a.long_rows[li];
-    const int32_t b = a.ptr[row], e = a.ptr[row + 1];
-    const int32_t pieces = (e - b + SPLIT - 1) / SPLIT;
-    // first piece of this row that falls to this group
-    int32_t first = (group - turn) % groups;
-    if (first < 0) first += groups;
-    for (int32_t pc = first; pc < pieces; pc += groups) {
-      const int32_t pb = b + pc * SPLIT;
-      const int32_t pe = (pb + SPLIT < e) ? pb + SPLIT : e;
-      row_piece<G, VEC>(a, row, pb, pe, gl, true);
+  const int32_t queued = static_cast<int32_t>(a.ctrl[CTRL_PACKED + 1]);
+  const int32_t total = static_cast<int32_t>(a.ctrl[CTRL_PACKED]);
+  const int panels = a.w / (G * VEC);
+  for (int32_t id = group; id < total; id += groups) {
+    int32_t lo = 0, hi = queued;  // long_rows[lo].y <= id < long_rows[hi].y
+    while (hi - lo > 1) {
+      const int32_t mid = (lo + hi) >> 1;
+      if (a.long_rows[mid].y <= id)
+        lo = mid;
+      else
+        hi = mid;
     }
-    turn = (turn + pieces) % groups;
+    const int2 q = a.long_rows[lo];
+    const int32_t b = a.ptr[q.x], e = a.ptr[q.x + 1];
+    const int32_t pb = b + (id - q.y) * SPLIT;
+    const int32_t pe = pb + SPLIT < e ? pb + SPLIT : e;
+    for (int panel = 0; panel < panels; ++panel) {
+      const int32_t col0 = panel * G * VEC + gl * VEC;
+      float acc[VEC];
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) acc[v] = 0.0f;
+      for (int32_t p = pb; p < pe; p += 4) fma4<G, VEC>(a, p, pe - p < 4 ? pe - p : 4, col0, acc);
+      store_c<VEC>(a.C + static_cast<size_t>(q.x) * a.w + col0, acc, true);
+    }
   }
 }
 
 template <int G, int VEC>
 bool launch_variant(Context &ctx, const SpmmArgs &a) {
   const int per_warp = 32 / G;
-  int64_t warps = (static_cast<int64_t>(a.n) + per_warp - 1) / per_warp;
-  int64_t blocks = (warps * 32 + M_THREADS - 1) / M_THREADS;
-  const int64_t cap = static_cast<int64_t>(ctx.num_sms) * 32;
-  if (blocks > cap) blocks = cap;
-  if (blocks < 1) blocks = 1;
-  spmm_rows_kernel<G, VEC><<<static_cast<int>(blocks), M_THREADS, 0, ctx.stream>>>(a);
+  if (a.w == G * VEC) {  // one panel: persistent groups, a few waves worth of them
+    spmm_rows_kernel<G, VEC><<<ctx.num_sms * 8, M_THREADS, 0, ctx.stream>>>(a);
+  } else {
+    int64_t warps = (static_cast<int64_t>(a.n) + per_warp - 1) / per_warp;
+    int64_t blocks = (warps * 32 + M_THREADS - 1) / M_THREADS;
+    const int64_t cap = static_cast<int64_t>(ctx.num_sms) * 32;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    spmm_panel_kernel<G, VEC><<<static_cast<int>(blocks), M_THREADS, 0, ctx.stream>>>(a);
+  }
   CSG_CUDA(cudaGetLastError());
-  spmm_long_kernel<G, VEC><<<ctx.num_sms * 4, M_THREADS, 0, ctx.stream>>>(a);
+  spmm_long_kernel<G, VEC><<<ctx.num_sms * 8, M_THREADS, 0, ctx.stream>>>(a);
   CSG_CUDA(cudaGetLastError());
   count_launches(2);
   return true;
@@ -181,14 +257,14 @@ bool launch_spmm(Context &ctx, int32_t n, int32_t nnz, int32_t w, const int32_t 
   a.val = d_val;
   a.B = d_B;
   a.C = d_C;
-  // queue of rows longer than SPLIT (at most nnz / SPLIT of them)
+  // scratch: counters and the queue of rows longer than SPLIT (at most nnz / SPLIT of them)
   Arena ar;
-  const size_t o_cnt = ar.take(256);
-  const size_t o_rows = ar.take(sizeof(int32_t) * (static_cast<size_t>(nnz) / SPLIT + 1));
+  const size_t o_ctrl = ar.take(sizeof(uint32_t) * CTRL_SCRATCH_WORDS);
+  const size_t o_rows = ar.take(sizeof(int2) * (static_cast<size_t>(nnz) / SPLIT + 1));
   if (!ensure_workspace(ctx, ar.off)) return false;
-  a.long_count = reinterpret_cast<uint32_t *>(ctx.ws + o_cnt);
-  a.long_rows = reinterpret_cast<int32_t *>(ctx.ws + o_rows);
-  CSG_CUDA(cudaMemsetAsync(a.long_count, 0, sizeof(uint32_t), ctx.stream));
+  a.ctrl = reinterpret_cast<uint32_t *>(ctx.ws + o_ctrl);
+  a.long_rows = reinterpret_cast<int2 *>(ctx.ws + o_rows);
+  CSG_CUDA(cudaMemsetAsync(a.ctrl, 0, sizeof(uint32_t) * CTRL_SCRATCH_WORDS, ctx.stream));
 
   const bool al16 = (reinterpret_cast<uintptr_t>(d_B) % 16 == 0) && (reinterpret_cast<uintptr_t>(d_C) % 16 == 0);
   if (w % 128 == 0 && al16) return launch_variant<32, 4>(ctx, a);
@@ -215,18 +291,18 @@ bool launch_spmm(Context &ctx, int32_t n, int32_t nnz, int32_t w, const int32_t 
 // cudaMalloc / cudaFree stall every stream of the device.  For them the queue of
 // long rows -- the only scratch the SpMM kernels need -- lives in a fixed array
 // that is part of the loaded library image, so every GPU that loads the library
-// holds these 256 KiB until the process exits.
+// holds these 512 KiB until the process exits.
 //
 // The array is shared by every call in the process and keeps what the last call
-// left in it; the call clears the one counter that must start at zero.  Two calls
+// left in it; the call clears the counters that must start at zero.  Two calls
 // whose kernels can overlap on the same GPU (different streams) would race on it.
 namespace csg {
 namespace {
 
-constexpr int STATIC_MAX_LONG_ROWS = 65536;  // queue capacity
-constexpr int STATIC_QUEUE_OFFSET = 64;      // words; the counter owns the first 256 bytes
+constexpr int STATIC_MAX_LONG_ROWS = 65536;  // queue capacity (entries of 8 bytes)
+constexpr int STATIC_QUEUE_OFFSET = CTRL_SCRATCH_WORDS;  // words; counters own the first 256 bytes
 static __device__ __align__(256) uint32_t g_spmm_static_scratch[STATIC_QUEUE_OFFSET +
-                                                                STATIC_MAX_LONG_ROWS];
+                                                                2 * STATIC_MAX_LONG_ROWS];
 
 // In host code the symbol above is only a stand-in, not a device address: the real
 // address is asked for once per device, with that device current.
@@ -268,9 +344,10 @@ bool run_spmm_static(int32_t n, int32_t nnz, int32_t w, const int32_t *d_ptr, co
   a.val = d_val;
   a.B = d_B;
   a.C = d_C;
-  a.long_count = scratch;
-  a.long_rows = reinterpret_cast<int32_t *>(scratch + STATIC_QUEUE_OFFSET);
-  CSG_CUDA(cudaMemsetAsync(a.long_count, 0, sizeof(uint32_t), stream));  // last call's count
+  a.ctrl = scratch;
+  a.long_rows = reinterpret_cast<int2 *>(scratch + STATIC_QUEUE_OFFSET);
+  // the counters keep the previous call's values: clear them (the queue is overwritten)
+  CSG_CUDA(cudaMemsetAsync(a.ctrl, 0, sizeof(uint32_t) * CTRL_SCRATCH_WORDS, stream));
   const bool al16 = (reinterpret_cast<uintptr_t>(d_B) % 16 == 0) &&
                     (reinterpret_cast<uintptr_t>(d_C) % 16 == 0);
   if (w % 128 == 0 && al16) return launch_variant<32, 4>(tmp, a);

@@ -149,7 +149,7 @@ SPORDER_API int32_t sporder_spmm_async(sporder_context_t ctx, int32_t n, int32_t
 /* SpMM for callers that must not trigger a device allocation (no counterpart in the
  * reference).  Same product as sporder_spmm, but it takes no context and calls no
  * cudaMalloc / cudaFree or allocating routine: the queue of long rows sits in a fixed
- * 256 KiB array inside the library image (held by every GPU that loads the library
+ * 512 KiB array inside the library image (held by every GPU that loads the library
  * until the process exits).  Meant for hosts that gave all device memory to their own
  * pool, or that ban driver allocations on their request path because those stall the
  * whole device.
