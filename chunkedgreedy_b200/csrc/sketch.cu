@@ -68,6 +68,12 @@ struct Sketch {
   int32_t gcell;       // its cell
   uint32_t l1w, l2w;   // this lane's smallest and second smallest weight (bits) ...
   int32_t l1c, l2c;    // ... and their cells, ordered by (weight, cell)
+  int32_t lane;        // read once through volatile asm: a re-read of the special
+                       // register inside the dependent chain costs ~25 cycles each time
+
+  __device__ __forceinline__ void bind_lane() {
+    asm volatile("mov.u32 %0, %%laneid;" : "=r"(lane));
+  }
 
   __device__ __forceinline__ void clear() {
 #pragma unroll
@@ -105,7 +111,7 @@ struct Sketch {
   __device__ __forceinline__ void find_victim(uint32_t lw, int32_t lc, uint32_t &vmin, int32_t &vown,
                                               int32_t &vcell) const {
     vmin = __reduce_min_sync(FULL, lw);
-    const uint32_t t = (lw == vmin) ? static_cast<uint32_t>((lc << 5) | lane_id()) : 0xFFFFFFFFu;
+    const uint32_t t = (lw == vmin) ? static_cast<uint32_t>((lc << 5) | lane) : 0xFFFFFFFFu;
     const uint32_t win = __reduce_min_sync(FULL, t);
     vown = static_cast<int32_t>(win & 31u);
     vcell = static_cast<int32_t>(win >> 5);
@@ -122,20 +128,20 @@ struct Sketch {
 #pragma unroll
     for (int c = 0; c < CELLS; ++c) hit_cell = (key[c] == s) ? c : hit_cell;
     const uint32_t hs = __reduce_min_sync(
-        FULL, hit_cell >= 0 ? static_cast<uint32_t>(lane_id() * CELLS + hit_cell) : 0xFFFFFFFFu);
+        FULL, hit_cell >= 0 ? static_cast<uint32_t>(lane * CELLS + hit_cell) : 0xFFFFFFFFu);
     return static_cast<int32_t>(hs);
   }
 
   __device__ __forceinline__ void add_weight(int32_t slot, float a) {
     const int hl = slot / CELLS, hc = slot % CELLS;
-    const bool me = lane_id() == hl;
+    const bool me = lane == hl;
 #pragma unroll
     for (int c = 0; c < CELLS; ++c) w[c] = (me & (c == hc)) ? w[c] + a : w[c];
   }
 
   __device__ __forceinline__ void put(int32_t slot, int32_t s, float wv) {
     const int ol = slot / CELLS, oc = slot % CELLS;
-    const bool me = lane_id() == ol;
+    const bool me = lane == ol;
 #pragma unroll
     for (int c = 0; c < CELLS; ++c) {
       const bool p = me & (c == oc);
@@ -163,7 +169,6 @@ struct Sketch {
   // beside the reductions instead of in front of them.  Written with selects only: a
   // lane-divergent branch here costs more than the rest of the step.
   __device__ __forceinline__ void add_full(int32_t s, float a) {
-    const int lane = lane_id();
     const bool own = lane == gown;
     const float wnew = __uint_as_float(gmin) + a;
     const uint32_t nb = __float_as_uint(wnew);
@@ -235,7 +240,6 @@ struct Sketch {
   // writes the valid prefix of the row's k entries (the table is pre-zeroed)
   __device__ __forceinline__ void select_top_k(int32_t k, uint64_t *out, int32_t row_base) {
     local_sort_descending();
-    const int lane = lane_id();
     int pos = 0;
     uint64_t mine = 0;
     int i = 0;
@@ -449,6 +453,7 @@ __global__ void __launch_bounds__(S_THREADS) sketch_kernel(SketchArgs a) {
   int32_t *bs = ring_s[warp];
   float *ba = ring_a[warp];
   Sketch<CELLS> sk;
+  sk.bind_lane();
   Producer<S_RING> prod(a);
   for (;;) {
     uint32_t item = 0;
@@ -476,13 +481,17 @@ __device__ __forceinline__ void pair_barrier(int pair) {
 }
 
 // Consumer and producer of one heavy row.  Each is compiled as a function of its own, with
-// its state created inside it, so the consumer's dependent chain is scheduled and
-// register-allocated as if it were alone in the kernel.
+// its state created inside it.  The consumer's loop is a dependent chain whose length
+// decides the run time of the whole call, and how the compiler schedules it turned out to
+// depend on what else lives in the same function: with the top-k selection (or any
+// register-staged prefetch) next to it, a step takes 1.5x longer.  So the loop stands alone:
+// it leaves the finished sketch in shared memory and the top-k selection runs as a
+// separate function afterwards.
 template <int CELLS>
-__device__ __noinline__ void heavy_consumer(const SketchArgs &a, const int32_t *ring_s,
-                                            const float *ring_a, int pair, int32_t r,
-                                            uint32_t total) {
+__device__ __forceinline__ void heavy_consumer(const int32_t *ring_s, const float *ring_a, int pair,
+                                            uint32_t total, int32_t *state) {
   Sketch<CELLS> sk;
+  sk.bind_lane();
   sk.clear();
   const uint32_t buffers = (total + H_RING - 1) / H_RING;
   for (uint32_t b = 0; b < buffers; ++b) {
@@ -490,6 +499,26 @@ __device__ __noinline__ void heavy_consumer(const SketchArgs &a, const int32_t *
     const uint32_t left = total - b * H_RING;
     consume<CELLS>(sk, ring_s + (b & 1) * H_RING, ring_a + (b & 1) * H_RING,
                    static_cast<int>(left < H_RING ? left : H_RING));
+  }
+  const int lane = lane_id();
+#pragma unroll
+  for (int c = 0; c < CELLS; ++c) {
+    state[(2 * c) * 32 + lane] = sk.key[c];
+    state[(2 * c + 1) * 32 + lane] = __float_as_int(sk.w[c]);
+  }
+  __syncwarp();
+}
+
+template <int CELLS>
+__device__ __noinline__ void heavy_top_k(const SketchArgs &a, int32_t r, const int32_t *state) {
+  Sketch<CELLS> sk;
+  sk.bind_lane();
+  sk.clear();
+  const int lane = lane_id();
+#pragma unroll
+  for (int c = 0; c < CELLS; ++c) {
+    sk.key[c] = state[(2 * c) * 32 + lane];
+    sk.w[c] = __int_as_float(state[(2 * c + 1) * 32 + lane]);
   }
   sk.select_top_k(a.k, a.table + static_cast<size_t>(r) * a.k, a.row_base);
 }
@@ -511,13 +540,17 @@ __device__ __noinline__ void heavy_producer(const SketchArgs &a, int32_t *ring_s
 // pair barrier the same number of times; neither waits on anything else.
 template <int CELLS>
 __global__ void __launch_bounds__(S_THREADS, 1) sketch_heavy_kernel(SketchArgs a) {
-  extern __shared__ __align__(16) unsigned char heavy_smem[];
+  extern __shared__ __align__(16) unsigned char heavy_pad[];  // only there to fill the SM
+  __shared__ int32_t hring_s[2][2 * H_RING];
+  __shared__ float hring_a[2][2 * H_RING];
   __shared__ uint32_t pair_item[2];
+  __shared__ int32_t pair_state[2][2 * CELLS * 32];  // finished sketch, for the top-k step
   const int lane = lane_id(), warp = threadIdx.x >> 5;
   const int pair = warp >> 1;
   const bool consumer = (warp & 1) == 0;
-  int32_t *ring_s = reinterpret_cast<int32_t *>(heavy_smem) + pair * (4 * H_RING);
-  float *ring_a = reinterpret_cast<float *>(ring_s + 2 * H_RING);
+  int32_t *ring_s = hring_s[pair];
+  float *ring_a = hring_a[pair];
+  if (heavy_pad[0] == 255 && a.n < 0) return;  // keeps the padding referenced
   const uint32_t heavy = a.ctrl[CTRL_HEAVY_ROWS];
   for (;;) {
     if (consumer && lane == 0) pair_item[pair] = atomicAdd(&a.ctrl[CTRL_HEAVY_TICKET], 1u);
@@ -529,9 +562,10 @@ __global__ void __launch_bounds__(S_THREADS, 1) sketch_heavy_kernel(SketchArgs a
     const int32_t rb = a.ptr[r], re = a.ptr[r + 1];
     if (!row_bounds_ok(a, rb, re)) continue;
     const uint32_t total = a.row_work[r];
-    if (consumer)
-      heavy_consumer<CELLS>(a, ring_s, ring_a, pair, r, total);
-    else
+    if (consumer) {
+      heavy_consumer<CELLS>(ring_s, ring_a, pair, total, pair_state[pair]);
+      heavy_top_k<CELLS>(a, r, pair_state[pair]);
+    } else
       heavy_producer(a, ring_s, ring_a, pair, r, rb, re, total);
   }
 }
@@ -541,7 +575,8 @@ bool launch_cells(Context &ctx, const SketchArgs &a) {
   // heavy rows on the context's stream, the rest beside them on the helper stream
   CSG_CUDA(cudaEventRecord(ctx.ev[5], ctx.stream));
   CSG_CUDA(cudaStreamWaitEvent(ctx.aux_stream, ctx.ev[5], 0));
-  const int heavy_smem = ctx.smem_optin - 1024;  // the whole SM: nothing else is placed there
+  // dynamic padding on top of the static rings: the whole SM, nothing else fits
+  const int heavy_smem = ctx.smem_optin - 1024 - 2 * 2 * CELLS * 32 * 4 - 2 * 2 * H_RING * 8;
   CSG_CUDA(cudaFuncSetAttribute(sketch_heavy_kernel<CELLS>,
                                 cudaFuncAttributeMaxDynamicSharedMemorySize, heavy_smem));
   sketch_heavy_kernel<CELLS><<<ctx.num_sms, S_THREADS, heavy_smem, ctx.stream>>>(a);
