@@ -116,6 +116,15 @@ bool plan_scratch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, uint
   const size_t tiles_max = z / 4096 + heavy_max + 1;
   const size_t o_hc = ar.take(4 * heavy_max), o_htb = ar.take(4 * (heavy_max + 1));
   const size_t o_th = ar.take(4 * 256 * tiles_max), o_db = ar.take(4 * 256 * heavy_max);
+  // streams of the heaviest rows: at most 2^27 entries (1 GiB), less for small inputs
+  const size_t span = static_cast<size_t>(p.chunk < n ? p.chunk : n);
+  size_t cap = z * span;
+  if (cap > (size_t(1) << 27)) cap = size_t(1) << 27;
+  const size_t hmax = cap / (size_t(1) << (SKETCH_HEAVY_BUCKET - 1)) + 1;
+  const size_t o_hs = ar.take(8 * cap), o_ho = ar.take(4 * (hmax + 1));
+  const size_t o_hst = ar.take(4 * hmax * 2 * (p.M / 32) * 32);
+  const size_t pmax = z / 2048 + hmax + 1;  // slices of 2048 columns
+  const size_t o_pb = ar.take(4 * (hmax + 2)), o_po = ar.take(4 * (pmax + 1));
   const size_t o_table = user_table ? 0 : ar.take(8 * static_cast<size_t>(n) * p.k);
   if (!ensure_workspace(ctx, ar.off)) return false;
   s->keyA = reinterpret_cast<uint32_t *>(ctx.ws + o_keyA);
@@ -129,6 +138,13 @@ bool plan_scratch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, uint
   s->row_list = reinterpret_cast<int32_t *>(ctx.ws + o_list);
   s->ctrl = reinterpret_cast<uint32_t *>(ctx.ws + o_ctrl);
   s->table = user_table ? user_table : reinterpret_cast<uint64_t *>(ctx.ws + o_table);
+  s->hstream = reinterpret_cast<int2 *>(ctx.ws + o_hs);
+  s->heavy_off = reinterpret_cast<uint32_t *>(ctx.ws + o_ho);
+  s->heavy_state = reinterpret_cast<int32_t *>(ctx.ws + o_hst);
+  s->part_base = reinterpret_cast<uint32_t *>(ctx.ws + o_pb);
+  s->part_off = reinterpret_cast<uint32_t *>(ctx.ws + o_po);
+  s->stream_cap = static_cast<uint32_t>(cap);
+  s->heavy_max = static_cast<uint32_t>(hmax);
   s->heavy_chunk = reinterpret_cast<int32_t *>(ctx.ws + o_hc);
   s->heavy_tile_base = reinterpret_cast<int32_t *>(ctx.ws + o_htb);
   s->tile_hist = reinterpret_cast<uint32_t *>(ctx.ws + o_th);
@@ -227,8 +243,6 @@ sporder_context_t sporder_context_create(void) {
   if ((e = cudaStreamCreateWithFlags(&c.own_stream, cudaStreamNonBlocking)) != cudaSuccess)
     return fail(e, "cudaStreamCreate");
   c.stream = c.own_stream;
-  if ((e = cudaStreamCreateWithFlags(&c.aux_stream, cudaStreamNonBlocking)) != cudaSuccess)
-    return fail(e, "cudaStreamCreate");
   cudaDeviceGetAttribute(&c.num_sms, cudaDevAttrMultiProcessorCount, c.device);
   cudaDeviceGetAttribute(&c.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, c.device);
   for (auto &ev : c.ev)
@@ -247,7 +261,6 @@ void sporder_context_destroy(sporder_context_t h) {
   for (auto &ev : c.ev)
     if (ev) cudaEventDestroy(ev);
   if (c.h_pinned) cudaFreeHost(c.h_pinned);
-  if (c.aux_stream) cudaStreamDestroy(c.aux_stream);
   if (c.own_stream) cudaStreamDestroy(c.own_stream);
   delete h;
 }

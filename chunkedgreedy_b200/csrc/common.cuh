@@ -44,7 +44,6 @@ struct Context {
   int device = 0;
   cudaStream_t stream = nullptr;  // stream every launch of this context uses
   cudaStream_t own_stream = nullptr;
-  cudaStream_t aux_stream = nullptr;  // helper stream for work that runs beside `stream`
   int num_sms = 0;
   int smem_optin = 0;  // max dynamic shared memory per block (opt-in)
   char *ws = nullptr;  // device workspace
@@ -88,6 +87,12 @@ struct CsgScratch {
   uint32_t *ctrl;  // [0]=chunk ticket [1]=row ticket [2]=rows listed [3..] see CTRL_* below
   uint64_t *table;  // n*k packed top-k entries
   uint32_t *gbitmaps;  // greedy bitmaps when they do not fit shared memory, else nullptr
+  // materialised candidate streams of the heaviest rows (see sketch.cu)
+  int2 *hstream;
+  uint32_t *heavy_off;
+  int32_t *heavy_state;
+  uint32_t stream_cap, heavy_max;
+  uint32_t *part_base, *part_off;
   // tiled sort of heavy chunks (see transpose.cu)
   int32_t *heavy_chunk, *heavy_tile_base;
   uint32_t *tile_hist, *digit_base;
@@ -100,12 +105,13 @@ enum {
   CTRL_HEAVY_COUNT = 4,    // chunks sorted by the tiled path
   CTRL_HEAVY_TILES = 5,    // their tiles
   CTRL_HEAVY_ROWS = 6,     // rows at the head of row_list that the heavy sketch kernel takes
-  CTRL_HEAVY_TICKET = 7,
-  CTRL_BUCKET_COUNT = 8,   // 33 entries
-  CTRL_BUCKET_BASE = 48,   // 33 entries
-  CTRL_BUCKET_FILL = 88,   // 33 entries
-  CTRL_STATS = 128,        // see stats.cu
-  CTRL_WORDS = 160
+  CTRL_HEAVY_TICKET = 7,   // and the word after it: a second ticket
+  CTRL_HEAVY_PARTS = 9,    // column slices of the heavy rows
+  CTRL_BUCKET_COUNT = 16,  // 33 entries
+  CTRL_BUCKET_BASE = 56,   // 33 entries
+  CTRL_BUCKET_FILL = 96,   // 33 entries
+  CTRL_STATS = 136,        // see greedy.cu (8-byte aligned)
+  CTRL_WORDS = 168
 };
 
 constexpr int SKETCH_HEAVY_BUCKET = 17;  // rows streaming >= 65536 candidates are "heavy"

@@ -25,12 +25,14 @@
 //    is computed ahead of time from each lane's cached two smallest weights (see
 //    Sketch::add_full);
 //  * the rows with the longest streams set the run time of the whole call, and a warp
-//    that shares its scheduler with seven others takes 1.6x longer per step.  Those
-//    rows therefore go to a kernel of their own (sketch_heavy_kernel): one block per
-//    SM holding all of its shared memory, so nothing else is scheduled there, and in
-//    it a producer warp and a consumer warp per row, double-buffered through shared
-//    memory.  All other rows run beside it, on another stream, at full occupancy with
-//    one warp doing both jobs.
+//    that shares its scheduler with seven others takes 1.6x longer per step.  Those rows
+//    (65536 stream elements or more) take a path of their own: their streams are written
+//    out to memory by the whole grid (heavy_expand_kernel, one warp per 2048 columns),
+//    then heavy_consume_kernel runs one warp per row and one warp per scheduler - one
+//    block per SM, kept alone there by its shared-memory request - doing nothing but the
+//    dependent chain.  The kernel of all other rows follows as a programmatic dependent
+//    launch: it starts as soon as the chain kernel's blocks are running and fills the SMs
+//    that kernel leaves or frees.
 #include "common.cuh"
 
 namespace csg {
@@ -40,7 +42,7 @@ namespace {
 constexpr int S_WARPS = 4;
 constexpr int S_THREADS = 32 * S_WARPS;
 constexpr int S_RING = 256;    // stream elements per batch, light rows
-constexpr int H_RING = 512;    // stream elements per buffer, heavy rows (two buffers per row)
+constexpr int H_PART = 2048;   // columns of a heavy row expanded by one warp
 constexpr int S_LONG = 48;     // groups with at least this many pending entries are copied by the whole warp
 
 struct SketchArgs {
@@ -53,6 +55,13 @@ struct SketchArgs {
   const uint32_t *row_work;
   uint32_t *ctrl;
   uint64_t *table;
+  // materialised streams of the heavy rows
+  int2 *hstream;
+  uint32_t *heavy_off;
+  int32_t *heavy_state;
+  uint32_t stream_cap, heavy_max;
+  uint32_t *part_base;  // first part of each heavy row, plus the total
+  uint32_t *part_off;   // per part: entries it produces, then its offset in hstream
 };
 
 // The sketch of one row: CELLS slots per lane, all in registers.  Slot (lane, cell) is
@@ -298,11 +307,13 @@ struct Producer {
     grank = nrank;
     done = 0;
   }
-  __device__ __forceinline__ void begin(int32_t row, int32_t row_begin, int32_t row_end) {
+  // columns [row_begin, row_end) of row `row` (CSR positions), which has row_size entries
+  __device__ __forceinline__ void begin(int32_t row, int32_t row_begin, int32_t row_end,
+                                        int32_t row_size) {
     r = row;
     rb = row_begin;
     re = row_end;
-    rs = re - rb;
+    rs = row_size;
     pb = rb;
     load_next(pb + lane_id());
     take_window();
@@ -424,6 +435,7 @@ __device__ __forceinline__ void consume(Sketch<CELLS> &sk, const int32_t *bs, co
   if (t < cnt) {  // full sketch: the dependent chain, next element requested one step ahead
     int32_t ns = bs[t];
     float na = ba[t];
+#pragma unroll 1
     for (; t < cnt; ++t) {
       const int32_t cs = ns;
       const float cf = na;
@@ -445,7 +457,7 @@ __device__ __forceinline__ bool row_bounds_ok(const SketchArgs &a, int32_t rb, i
 
 // All rows below the heavy threshold: one warp per row, producing and consuming in turn.
 template <int CELLS>
-__global__ void __launch_bounds__(S_THREADS) sketch_kernel(SketchArgs a) {
+__global__ void __launch_bounds__(S_THREADS) sketch_kernel(SketchArgs a, int after_primary) {
   __shared__ int32_t ring_s[S_WARPS][S_RING];
   __shared__ float ring_a[S_WARPS][S_RING];
   const int lane = lane_id(), warp = threadIdx.x >> 5;
@@ -464,7 +476,7 @@ __global__ void __launch_bounds__(S_THREADS) sketch_kernel(SketchArgs a) {
     const int32_t rb = a.ptr[r], re = a.ptr[r + 1];
     if (!row_bounds_ok(a, rb, re)) continue;
     sk.clear();
-    prod.begin(r, rb, re);
+    prod.begin(r, rb, re, re - rb);
     for (;;) {
       const int cnt = prod.produce(bs, ba);
       if (cnt == 0) break;
@@ -473,122 +485,286 @@ __global__ void __launch_bounds__(S_THREADS) sketch_kernel(SketchArgs a) {
     }
     sk.select_top_k(a.k, a.table + static_cast<size_t>(r) * a.k, a.row_base);
   }
+  // Launched as the programmatic dependent of the heavy-chain kernel, this kernel starts
+  // while that one is still running; it must not be seen as finished before it.
+  if (after_primary) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
-// barrier of one producer/consumer pair (64 threads); ids 1 and 2
-__device__ __forceinline__ void pair_barrier(int pair) {
-  asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory");
-}
-
-// Consumer and producer of one heavy row.  Each is compiled as a function of its own, with
-// its state created inside it.  The consumer's loop is a dependent chain whose length
-// decides the run time of the whole call, and how the compiler schedules it turned out to
-// depend on what else lives in the same function: with the top-k selection (or any
-// register-staged prefetch) next to it, a step takes 1.5x longer.  So the loop stands alone:
-// it leaves the finished sketch in shared memory and the top-k selection runs as a
-// separate function afterwards.
-template <int CELLS>
-__device__ __forceinline__ void heavy_consumer(const int32_t *ring_s, const float *ring_a, int pair,
-                                            uint32_t total, int32_t *state) {
-  Sketch<CELLS> sk;
-  sk.bind_lane();
-  sk.clear();
-  const uint32_t buffers = (total + H_RING - 1) / H_RING;
-  for (uint32_t b = 0; b < buffers; ++b) {
-    pair_barrier(pair);  // buffer b is ready
-    const uint32_t left = total - b * H_RING;
-    consume<CELLS>(sk, ring_s + (b & 1) * H_RING, ring_a + (b & 1) * H_RING,
-                   static_cast<int>(left < H_RING ? left : H_RING));
+// ---- heavy rows through materialised streams ------------------------------------------
+// offsets of the heavy rows' streams in hstream; trims the heavy set to what fits
+__global__ void __launch_bounds__(1024) heavy_offsets_kernel(SketchArgs a) {
+  __shared__ unsigned long long sm[32];
+  __shared__ unsigned long long carry_s;
+  __shared__ uint32_t count_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t H = a.ctrl[CTRL_HEAVY_ROWS];
+  if (H > a.heavy_max) H = a.heavy_max;
+  if (threadIdx.x == 0) {
+    carry_s = 0;
+    count_s = H;
   }
-  const int lane = lane_id();
+  __syncthreads();
+  for (uint32_t base = 0; base < H; base += 1024) {
+    const uint32_t i = base + threadIdx.x;
+    uint32_t v = 0, np = 0;
+    if (i < H) {
+      const int32_t r = a.row_list[i];
+      v = a.row_work[r];
+      np = static_cast<uint32_t>((a.ptr[r + 1] - a.ptr[r] + H_PART - 1) / H_PART);
+    }
+    // parts first (same scan, second value packed in the high half of 64 bits)
+    unsigned long long pk = (static_cast<unsigned long long>(np) << 43) | v;  // sums: < 2^21 parts, < 2^43 entries
+    unsigned long long incl = pk;
 #pragma unroll
-  for (int c = 0; c < CELLS; ++c) {
-    state[(2 * c) * 32 + lane] = sk.key[c];
-    state[(2 * c + 1) * 32 + lane] = __float_as_int(sk.w[c]);
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned long long t = __shfl_up_sync(FULL, incl, off);
+      if (lane >= off) incl += t;
+    }
+    if (lane == 31) sm[warp] = incl;
+    __syncthreads();
+    unsigned long long wbase = 0, tot = 0;
+    for (int w = 0; w < 32; ++w) {
+      const unsigned long long t = sm[w];
+      if (w < warp) wbase += t;
+      tot += t;
+    }
+    const unsigned long long carry = carry_s;
+    const unsigned long long excl = carry + wbase + incl - pk;
+    if (i < H) {
+      const unsigned long long e_off = excl & ((1ull << 43) - 1);
+      a.heavy_off[i] = static_cast<uint32_t>(e_off > 0xFFFFFFFFull ? 0xFFFFFFFFull : e_off);
+      a.part_base[i] = static_cast<uint32_t>(excl >> 43);
+      if (e_off + v > a.stream_cap) atomicMin(&count_s, i);  // first row that does not fit
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) carry_s = carry + tot;
+    __syncthreads();
   }
-  __syncwarp();
+  if (threadIdx.x == 0) {
+    const uint32_t Hc = count_s;
+    // parts of the rows that stay heavy: part_base[Hc] closes the table
+    if (Hc == H)
+      a.part_base[H] = static_cast<uint32_t>(carry_s >> 43);
+    // (when trimmed, part_base[Hc] already holds the first dropped row's base)
+    a.ctrl[CTRL_HEAVY_PARTS] = Hc == H ? static_cast<uint32_t>(carry_s >> 43) : a.part_base[Hc];
+    a.ctrl[CTRL_HEAVY_ROWS] = count_s;
+    a.ctrl[CTRL_ROW_TICKET] = count_s;  // the other rows' tickets start behind the heavy ones
+    a.ctrl[CTRL_HEAVY_TICKET] = 0;
+    a.ctrl[CTRL_HEAVY_TICKET + 1] = 0;
+  }
 }
 
-template <int CELLS>
-__device__ __noinline__ void heavy_top_k(const SketchArgs &a, int32_t r, const int32_t *state) {
-  Sketch<CELLS> sk;
-  sk.bind_lane();
-  sk.clear();
+// part -> (heavy row, column range).  Uniform over the warp.
+struct PartRef {
+  uint32_t item;
+  int32_t r, pb, pe, row_size;
+};
+__device__ __forceinline__ PartRef part_ref(const SketchArgs &a, uint32_t part, uint32_t heavy) {
+  uint32_t lo = 0, hi = heavy;  // part_base[lo] <= part < part_base[hi]
+  while (hi - lo > 1) {
+    const uint32_t mid = (lo + hi) >> 1;
+    if (a.part_base[mid] <= part)
+      lo = mid;
+    else
+      hi = mid;
+  }
+  PartRef p;
+  p.item = lo;
+  p.r = a.row_list[lo];
+  const int32_t rb = a.ptr[p.r], re = a.ptr[p.r + 1];
+  p.row_size = re - rb;
+  p.pb = rb + static_cast<int32_t>(part - a.part_base[lo]) * H_PART;
+  p.pe = p.pb + H_PART < re ? p.pb + H_PART : re;
+  if (rb < 0 || re < rb || re > a.nnz) {  // malformed row pointers: nothing to do
+    atomicExch(&a.ctrl[CTRL_BAD_INPUT], 1u);
+    p.pe = p.pb;
+  }
+  return p;
+}
+
+// stream entries every part (H_PART columns of a heavy row) will produce
+__global__ void __launch_bounds__(256) heavy_part_count_kernel(SketchArgs a) {
   const int lane = lane_id();
+  const uint32_t heavy = a.ctrl[CTRL_HEAVY_ROWS], parts = a.ctrl[CTRL_HEAVY_PARTS];
+  const uint32_t warps = (gridDim.x * blockDim.x) >> 5;
+  for (uint32_t part = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; part < parts; part += warps) {
+    const PartRef p = part_ref(a, part, heavy);
+    uint32_t cnt = 0;
+    for (int32_t q = p.pb + lane; q < p.pe; q += 32) {
+      const int32_t len = a.seg[q].y;
+      cnt += len >= 2 ? static_cast<uint32_t>(len - 1) : 0u;
+    }
 #pragma unroll
-  for (int c = 0; c < CELLS; ++c) {
-    sk.key[c] = state[(2 * c) * 32 + lane];
-    sk.w[c] = __int_as_float(state[(2 * c + 1) * 32 + lane]);
-  }
-  sk.select_top_k(a.k, a.table + static_cast<size_t>(r) * a.k, a.row_base);
-}
-
-__device__ __noinline__ void heavy_producer(const SketchArgs &a, int32_t *ring_s, float *ring_a,
-                                            int pair, int32_t r, int32_t rb, int32_t re,
-                                            uint32_t total) {
-  Producer<H_RING> prod(a);
-  prod.begin(r, rb, re);
-  const uint32_t buffers = (total + H_RING - 1) / H_RING;
-  for (uint32_t b = 0; b < buffers; ++b) {
-    prod.produce(ring_s + (b & 1) * H_RING, ring_a + (b & 1) * H_RING);
-    pair_barrier(pair);  // hand over buffer b; buffer b-1 has been consumed
+    for (int off = 16; off > 0; off >>= 1) cnt += __shfl_down_sync(FULL, cnt, off);
+    if (lane == 0) a.part_off[part] = cnt;
   }
 }
 
-// The heaviest rows: two (producer warp, consumer warp) pairs per block, one block per SM.
-// Both warps of a pair derive the number of buffers from row_work, so they meet at the
-// pair barrier the same number of times; neither waits on anything else.
-template <int CELLS>
-__global__ void __launch_bounds__(S_THREADS, 1) sketch_heavy_kernel(SketchArgs a) {
-  extern __shared__ __align__(16) unsigned char heavy_pad[];  // only there to fill the SM
-  __shared__ int32_t hring_s[2][2 * H_RING];
-  __shared__ float hring_a[2][2 * H_RING];
-  __shared__ uint32_t pair_item[2];
-  __shared__ int32_t pair_state[2][2 * CELLS * 32];  // finished sketch, for the top-k step
+// counts -> offsets (exclusive scan in place, one block)
+__global__ void __launch_bounds__(1024) heavy_part_scan_kernel(SketchArgs a) {
+  __shared__ uint32_t sm[32];
+  __shared__ uint32_t carry_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t parts = a.ctrl[CTRL_HEAVY_PARTS];
+  if (threadIdx.x == 0) carry_s = 0;
+  __syncthreads();
+  for (uint32_t base = 0; base < parts; base += 1024) {
+    const uint32_t i = base + threadIdx.x;
+    const uint32_t v = i < parts ? a.part_off[i] : 0u;
+    uint32_t incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t t = __shfl_up_sync(FULL, incl, off);
+      if (lane >= off) incl += t;
+    }
+    if (lane == 31) sm[warp] = incl;
+    __syncthreads();
+    uint32_t wbase = 0, tot = 0;
+    for (int w = 0; w < 32; ++w) {
+      const uint32_t t = sm[w];
+      if (w < warp) wbase += t;
+      tot += t;
+    }
+    const uint32_t carry = carry_s;
+    if (i < parts) a.part_off[i] = carry + wbase + incl - v;
+    __syncthreads();
+    if (threadIdx.x == 0) carry_s = carry + tot;
+    __syncthreads();
+  }
+}
+
+// one warp per part: its slice of the row's stream, written out in order
+__global__ void __launch_bounds__(S_THREADS) heavy_expand_kernel(SketchArgs a) {
+  __shared__ int32_t ring_s[S_WARPS][S_RING];
+  __shared__ float ring_a[S_WARPS][S_RING];
   const int lane = lane_id(), warp = threadIdx.x >> 5;
-  const int pair = warp >> 1;
-  const bool consumer = (warp & 1) == 0;
-  int32_t *ring_s = hring_s[pair];
-  float *ring_a = hring_a[pair];
-  if (heavy_pad[0] == 255 && a.n < 0) return;  // keeps the padding referenced
-  const uint32_t heavy = a.ctrl[CTRL_HEAVY_ROWS];
+  const uint32_t heavy = a.ctrl[CTRL_HEAVY_ROWS], parts = a.ctrl[CTRL_HEAVY_PARTS];
+  int32_t *bs = ring_s[warp];
+  float *ba = ring_a[warp];
+  Producer<S_RING> prod(a);
   for (;;) {
-    if (consumer && lane == 0) pair_item[pair] = atomicAdd(&a.ctrl[CTRL_HEAVY_TICKET], 1u);
-    pair_barrier(pair);
-    const uint32_t item = pair_item[pair];
-    pair_barrier(pair);  // both have read the ticket before the next one is written
+    uint32_t part = 0;
+    if (lane == 0) part = atomicAdd(&a.ctrl[CTRL_HEAVY_TICKET], 1u);
+    part = __shfl_sync(FULL, part, 0);
+    if (part >= parts) break;
+    const PartRef p = part_ref(a, part, heavy);
+    if (p.pe <= p.pb) continue;
+    int2 *out = a.hstream + a.part_off[part];
+    prod.begin(p.r, p.pb, p.pe, p.row_size);
+    for (;;) {
+      const int cnt = prod.produce(bs, ba);
+      if (cnt == 0) break;
+      for (int i = lane; i < cnt; i += 32) out[i] = make_int2(bs[i], __float_as_int(ba[i]));
+      out += cnt;
+      __syncwarp();
+    }
+  }
+}
+
+// The dependent chains: one warp per heavy row, one warp per scheduler (one block per SM,
+// kept alone there by its shared-memory request), reading the stream back in batches.
+// The finished sketch goes to memory; the top-k selection is a kernel of its own, because
+// with it in the same function the compiler schedules this loop 1.5x slower.
+template <int CELLS>
+__global__ void __launch_bounds__(S_THREADS, 1) heavy_consume_kernel(SketchArgs a) {
+  extern __shared__ __align__(16) unsigned char heavy_pad[];  // only there to fill the SM
+  __shared__ int32_t ring_s[S_WARPS][S_RING];
+  __shared__ float ring_a[S_WARPS][S_RING];
+  const int lane = lane_id(), warp = threadIdx.x >> 5;
+  if (heavy_pad[0] == 255 && a.n < 0) return;  // keeps the padding referenced
+  // every block of this grid is resident now (one per SM): let the kernel of the other
+  // rows, launched behind this one in the same stream, start on whatever is left
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const uint32_t heavy = a.ctrl[CTRL_HEAVY_ROWS];
+  int32_t *bs = ring_s[warp];
+  float *ba = ring_a[warp];
+  Sketch<CELLS> sk;
+  sk.bind_lane();
+  for (;;) {
+    uint32_t item = 0;
+    if (lane == 0) item = atomicAdd(&a.ctrl[CTRL_HEAVY_TICKET + 1], 1u);
+    item = __shfl_sync(FULL, item, 0);
     if (item >= heavy) break;
     const int32_t r = a.row_list[item];
-    const int32_t rb = a.ptr[r], re = a.ptr[r + 1];
-    if (!row_bounds_ok(a, rb, re)) continue;
     const uint32_t total = a.row_work[r];
-    if (consumer) {
-      heavy_consumer<CELLS>(ring_s, ring_a, pair, total, pair_state[pair]);
-      heavy_top_k<CELLS>(a, r, pair_state[pair]);
-    } else
-      heavy_producer(a, ring_s, ring_a, pair, r, rb, re, total);
+    const int2 *in = a.hstream + a.heavy_off[item];
+    sk.clear();
+    for (uint32_t base = 0; base < total; base += S_RING) {
+      const int cnt = static_cast<int>(total - base < S_RING ? total - base : S_RING);
+      for (int i = lane; i < cnt; i += 32) {
+        const int2 e = in[base + i];
+        bs[i] = e.x;
+        ba[i] = __int_as_float(e.y);
+      }
+      __syncwarp();
+      consume<CELLS>(sk, bs, ba, cnt);
+      __syncwarp();
+    }
+    int32_t *st = a.heavy_state + static_cast<size_t>(item) * (2 * CELLS * 32);
+#pragma unroll
+    for (int c = 0; c < CELLS; ++c) {
+      st[(2 * c) * 32 + lane] = sk.key[c];
+      st[(2 * c + 1) * 32 + lane] = __float_as_int(sk.w[c]);
+    }
+  }
+}
+
+template <int CELLS>
+__global__ void __launch_bounds__(S_THREADS) heavy_topk_kernel(SketchArgs a) {
+  const int lane = lane_id();
+  const uint32_t heavy = a.ctrl[CTRL_HEAVY_ROWS];
+  const uint32_t warps = (gridDim.x * blockDim.x) >> 5;
+  Sketch<CELLS> sk;
+  sk.bind_lane();
+  for (uint32_t item = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; item < heavy; item += warps) {
+    const int32_t *st = a.heavy_state + static_cast<size_t>(item) * (2 * CELLS * 32);
+    sk.clear();
+#pragma unroll
+    for (int c = 0; c < CELLS; ++c) {
+      sk.key[c] = st[(2 * c) * 32 + lane];
+      sk.w[c] = __int_as_float(st[(2 * c + 1) * 32 + lane]);
+    }
+    const int32_t r = a.row_list[item];
+    sk.select_top_k(a.k, a.table + static_cast<size_t>(r) * a.k, a.row_base);
   }
 }
 
 template <int CELLS>
 bool launch_cells(Context &ctx, const SketchArgs &a) {
-  // heavy rows on the context's stream, the rest beside them on the helper stream
-  CSG_CUDA(cudaEventRecord(ctx.ev[5], ctx.stream));
-  CSG_CUDA(cudaStreamWaitEvent(ctx.aux_stream, ctx.ev[5], 0));
-  // dynamic padding on top of the static rings: the whole SM, nothing else fits
-  const int heavy_smem = ctx.smem_optin - 1024 - 2 * 2 * CELLS * 32 * 4 - 2 * 2 * H_RING * 8;
-  CSG_CUDA(cudaFuncSetAttribute(sketch_heavy_kernel<CELLS>,
-                                cudaFuncAttributeMaxDynamicSharedMemorySize, heavy_smem));
-  sketch_heavy_kernel<CELLS><<<ctx.num_sms, S_THREADS, heavy_smem, ctx.stream>>>(a);
+  heavy_offsets_kernel<<<1, 1024, 0, ctx.stream>>>(a);
   CSG_CUDA(cudaGetLastError());
+  heavy_part_count_kernel<<<ctx.num_sms * 4, 256, 0, ctx.stream>>>(a);
+  CSG_CUDA(cudaGetLastError());
+  heavy_part_scan_kernel<<<1, 1024, 0, ctx.stream>>>(a);
+  CSG_CUDA(cudaGetLastError());
+  heavy_expand_kernel<<<ctx.num_sms * 8, S_THREADS, 0, ctx.stream>>>(a);
+  CSG_CUDA(cudaGetLastError());
+  const int pad = ctx.smem_optin - 1024 - 2 * S_WARPS * S_RING * 4;
+  CSG_CUDA(cudaFuncSetAttribute(heavy_consume_kernel<CELLS>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, pad));
+  heavy_consume_kernel<CELLS><<<ctx.num_sms, S_THREADS, pad, ctx.stream>>>(a);
+  CSG_CUDA(cudaGetLastError());
+  // The other rows run beside the heavy chains: their kernel follows in the same stream
+  // as a programmatic dependent launch, so its blocks are placed only after every block
+  // of the chain kernel is running (and has its SM to itself), and it fills the SMs that
+  // stay or fall free.  It waits for the chain kernel before it ends (see sketch_kernel).
   int per_sm = 0;
   CSG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sketch_kernel<CELLS>, S_THREADS, 0));
   if (per_sm < 1) per_sm = 1;
-  sketch_kernel<CELLS><<<ctx.num_sms * per_sm, S_THREADS, 0, ctx.aux_stream>>>(a);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ctx.num_sms * per_sm);
+  cfg.blockDim = dim3(S_THREADS);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = ctx.stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CSG_CUDA(cudaLaunchKernelEx(&cfg, sketch_kernel<CELLS>, a, 1));
+  heavy_topk_kernel<CELLS><<<ctx.num_sms, S_THREADS, 0, ctx.stream>>>(a);
   CSG_CUDA(cudaGetLastError());
-  CSG_CUDA(cudaEventRecord(ctx.ev[6], ctx.aux_stream));
-  CSG_CUDA(cudaStreamWaitEvent(ctx.stream, ctx.ev[6], 0));
-  count_launches(2);
+  count_launches(7);
   return true;
 }
 
@@ -608,6 +784,13 @@ bool launch_sketch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, con
   a.cand = s.cand;
   a.row_list = s.row_list;
   a.row_work = s.row_work;
+  a.hstream = s.hstream;
+  a.heavy_off = s.heavy_off;
+  a.heavy_state = s.heavy_state;
+  a.stream_cap = s.stream_cap;
+  a.heavy_max = s.heavy_max;
+  a.part_base = s.part_base;
+  a.part_off = s.part_off;
   a.ctrl = s.ctrl;
   a.table = s.table;
   // rows without candidates are never visited: their entries must read as empty
