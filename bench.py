@@ -49,9 +49,27 @@ def log(*a):
     print("[bench %7.1fs]" % (time.time() - T_START), *a, file=sys.stderr, flush=True)
 
 
-def load_workload(scale):
-    """The R-MAT matrix (host numpy int32 CSR), cached in /tmp between runs."""
+def load_workload(scale, name="rmat22"):
+    """The workload matrix (host numpy int32 CSR), cached in /tmp between runs.  `rmat22`
+    with another --scale is the same R-MAT recipe at that scale; the other names are the
+    remaining benchmark configurations at full size."""
     from chunkedgreedy_b200 import synth
+    if name != "rmat22":
+        cache = "/tmp/chunkedgreedy_b200_%s.npz" % name
+        if os.path.exists(cache):
+            try:
+                z = np.load(cache)
+                return z["ptr"], z["ind"], z["val"]
+            except Exception:
+                pass
+        w = synth.make_workload(name)
+        try:
+            tmp = cache + ".%d.tmp.npz" % os.getpid()
+            np.savez(tmp, ptr=w["ptr"], ind=w["ind"], val=w["val"])
+            os.replace(tmp, cache)
+        except Exception:
+            pass
+        return w["ptr"], w["ind"], w["val"]
     cache = "/tmp/chunkedgreedy_b200_rmat%d_seed3.npz" % scale
     if os.path.exists(cache):
         try:
@@ -184,7 +202,7 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     import oracle
-    ptr, ind, _ = load_workload(args.scale)
+    ptr, ind, _ = load_workload(args.scale, args.workload)
     n, nnz = ptr.size - 1, ind.size
     k = min(256, max(16, nnz // n))
     step, sample_nnz, desc = cpu_reference_rate(ptr, ind, k, args.cpu_budget,
@@ -211,8 +229,12 @@ def run_reference(args, rank, world):
 
 
 def workload_config(n, nnz, k, args):
-    return {"workload": "rmat scale %d ef16 a.57 b.19 c.19 d.05 dedup seed3; csg k=%d M=%d chunk=%d"
-                        % (args.scale, k, ((4 * k + 31) // 32) * 32, CHUNK),
+    names = {"rmat22": "rmat scale %d ef16 a.57 b.19 c.19 d.05 dedup seed3" % args.scale,
+             "zipf65k": "zipf-banded 65536 rows seed0", "stencil1024": "9-point stencil 1024^2 relabelled seed1",
+             "road2m": "road lattice 2M vertices relabelled seed2",
+             "rmat20gcn": "rmat scale 20 symmetrised + self loops, normalised, seed4"}
+    return {"workload": "%s; csg k=%d M=%d chunk=%d"
+                        % (names[args.workload], k, ((4 * k + 31) // 32) * 32, CHUNK),
             "n": int(n), "nnz": int(nnz), "parallelism": "row shards x%d" % args.gpus,
             "l2": "inputs and scratch (>1 GB) exceed L2; no explicit flush"}
 
@@ -225,7 +247,7 @@ def run_ours(args, rank, world, local_rank):
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    ptr, ind, val = load_workload(args.scale)
+    ptr, ind, val = load_workload(args.scale, args.workload)
     n, nnz = ptr.size - 1, ind.size
     k = csgdist.resolve_k(n, nnz, 0)
     bounds = csgdist.shard_bounds(ptr, CHUNK, world)
@@ -328,10 +350,12 @@ def run_ours(args, rank, world, local_rank):
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
         "stages_ms": stage,
-        "roofline": {"bound": "hbm", "kernel": "sketch_kernel (sketch + top-k)", "achieved": ach,
+        "roofline": {"bound": "hbm",
+                     "kernel": "sketch + top-k stage (heavy_expand, heavy_consume, sketch_kernel)",
+                     "achieved": ach,
                      "peak": hbm, "unit": "GB/s", "frac": ach / hbm, "peak_source": peak_src,
                      "algorithmic_bytes": int(b_sketch),
-                     "traffic": TRAFFIC_FROM_NCU.get("sketch_kernel")},
+                     "traffic": TRAFFIC_FROM_NCU.get(args.workload if args.scale == 22 else None)},
     }
     if world == 1 and not args.no_cpu_baseline:
         import oracle
@@ -341,19 +365,24 @@ def run_ours(args, rank, world, local_rank):
                                 "cores": oracle.num_threads(), "kind": "port", "sample": desc}
         log("cpu baseline done")
     if world == 1 and not args.no_ref_cuda:
-        line["reference_cuda"] = reference_cuda(d_ptr, d_ind, nnz)
+        from chunkedgreedy_b200 import synth
+        line["reference_cuda"] = reference_cuda(d_ptr, d_ind, nnz, synth.WORKLOADS[args.workload][2])
         log("reference cuda done", line["reference_cuda"])
     if world == 1 and not args.no_spmm:
         line["spmm"] = spmm_section(sp, ctx, d_ptr, d_ind, torch.from_numpy(val).to(dev), order,
                                     n, nnz, hbm)
+    if world == 1 and args.gcn:
+        line["gcn"] = gcn_section(d_ptr, d_ind, torch.from_numpy(val).to(dev), n, ctx,
+                                  args.gcn_epochs)
     print(json.dumps(line), flush=True)
 
 
-# per-launch DRAM traffic of the dominant kernel from an ncu capture (see profiles/)
+# DRAM bytes (read + write) of the sketch stage's kernels per csg call, from an ncu capture
+# of this command at full size (see profiles/)
 TRAFFIC_FROM_NCU = {}
 
 
-def reference_cuda(d_ptr, d_ind, nnz):
+def reference_cuda(d_ptr, d_ind, nnz, is_symmetric=False):
     """The reference's own CUDA library, built unchanged for sm_100a (oracle/_ref), on the
     same matrix with its benchmark protocol (one warm-up call, then the library's wall_ms;
     bench/reorder/reorder_bench/methods/sporder_csg.py:41-57)."""
@@ -362,10 +391,10 @@ def reference_cuda(d_ptr, d_ind, nnz):
         if not ref.available():
             return {"unavailable": "oracle/_ref/libsporder_ref.so not present"}
         import torch
-        ref.csg(d_ptr, d_ind, False)
+        ref.csg(d_ptr, d_ind, is_symmetric)
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=d_ptr.device)
         flush.zero_()
-        _, tm = ref.csg(d_ptr, d_ind, False, with_timing=True)
+        _, tm = ref.csg(d_ptr, d_ind, is_symmetric, with_timing=True)
         return {"value": nnz / (tm["wall_ms"] * 1e-3) / 1e6, "unit": "Mnnz/s", "timing_ms": tm,
                 "kind": "reference CUDA sources compiled for sm_100a, 1 GPU"}
     except Exception as e:  # never let the comparison leg break the bench line
@@ -402,6 +431,20 @@ def spmm_section(sp, ctx, d_ptr, d_ind, d_val, order, n, nnz, hbm, widths=(32, 1
     return out
 
 
+def gcn_section(d_ptr, d_ind, d_val, n, ctx, epochs):
+    """2-layer GCN (128 -> 128 -> 16, ReLU, full-batch SGD), features N(0,1), uniform labels,
+    seed 4: training on the matrix as given against reorder once + train on P A P^T."""
+    import torch
+    from chunkedgreedy_b200 import gcn
+    g = torch.Generator(device=d_ptr.device).manual_seed(4)
+    x = torch.randn((n, 128), device=d_ptr.device, generator=g)
+    y = torch.randint(0, 16, (n,), device=d_ptr.device, generator=g)
+    r = gcn.reorder_and_train(d_ptr, d_ind, d_val, x, y, hidden=128, classes=16, epochs=epochs,
+                              optimizer="sgd", ctx=ctx)
+    r.pop("order")
+    return r
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -409,6 +452,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--scale", type=int, default=22, help="R-MAT scale (22 = the named workload)")
+    ap.add_argument("--workload", default="rmat22",
+                    choices=["rmat22", "zipf65k", "stencil1024", "road2m", "rmat20gcn"],
+                    help="rmat22 is the bench workload; the others are the remaining configurations")
+    ap.add_argument("--gcn", action="store_true",
+                    help="also run the reorder-then-train GCN experiment (use with --workload rmat20gcn)")
+    ap.add_argument("--gcn-epochs", type=int, default=200)
     ap.add_argument("--cpu-budget", type=float, default=20.0,
                     help="seconds of CPU work the baseline sample is sized for")
     ap.add_argument("--no-cpu-baseline", action="store_true")

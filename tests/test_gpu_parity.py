@@ -246,3 +246,38 @@ def test_gcn_gradients_match_dense_reference_and_reordering_is_equivalent():
     a, b = res["original"]["final_loss"], res["reordered"]["final_loss"]
     assert abs(a - b) <= 1e-3 * max(1.0, abs(a))
     assert sorted(res["order"].cpu().tolist()) == list(range(n))
+
+
+@pytest.mark.parametrize("name", ["stencil1024", "road2m"])
+def test_full_size_streaming_workloads_bit_exact(name):
+    # benchmark configurations 2 and 3 at their full sizes (1.05 M / 2 M rows): the oracle
+    # finishes in seconds because relabelled meshes have almost no in-chunk candidates
+    sp = _sp()
+    from chunkedgreedy_b200 import synth
+    w = synth.make_workload(name)
+    order, table = sp.csg_table(_dev(w["ptr"]), _dev(w["ind"]), is_symmetric=True)
+    o_or, t_or = oracle.csg(w["ptr"], w["ind"], True, with_table=True)
+    assert np.array_equal(order.cpu().numpy(), o_or)
+    assert np.array_equal(table.cpu().numpy().view(np.uint64), t_or)
+
+
+def test_full_size_power_law_workload_properties():
+    # benchmark configuration 4 at scale 20 against the oracle, bit-exact, and the structural
+    # invariants of the reference's smoke test on the result (valid permutation, every chunk a
+    # permutation of its own rows that starts at the chunk's first row), plus the
+    # P A P^T round trip
+    sp = _sp()
+    from chunkedgreedy_b200 import synth
+    ptr, ind, val = synth.rmat(scale=20, seed=3)
+    n = ptr.size - 1
+    dp, di, dv = _dev(ptr), _dev(ind), _dev(val)
+    order = sp.chunk_similarity_greedy(dp, di)
+    assert np.array_equal(order.cpu().numpy(), oracle.csg(ptr, ind, False))
+    o = order.cpu().numpy().reshape(-1, 1024)
+    assert np.array_equal(o[:, 0], np.arange(0, n, 1024))
+    assert np.array_equal(np.sort(o, axis=1), np.arange(n).reshape(-1, 1024))
+    p2, i2, v2 = sp.reorder(dp, di, order, val=dv, symmetric=True)
+    inv = torch.empty_like(order)
+    inv[order.long()] = torch.arange(n, dtype=torch.int32, device="cuda")
+    p3, i3, v3 = sp.reorder(p2, i2, inv, val=v2, symmetric=True)
+    assert torch.equal(p3, dp) and torch.equal(i3, di) and torch.equal(v3, dv)
