@@ -223,6 +223,27 @@ def random_sparse(n, avg_deg, seed, symmetric=False, hub_cols=0, hub_frac=0.0,
     return ptr, ind, val
 
 
+def dense_block(n, row0, rows, cols, seed, ragged=0, noise_deg=0.0):
+    """``rows`` consecutive rows starting at ``row0`` that all hold columns ``[0, cols)``:
+    every such row streams ``cols * (rows - 1)`` candidates, enough for the heavy-row path
+    of the sketch stage at a few hundred rows.  With ``ragged`` > 0 row i stops
+    ``i % ragged`` columns short (unequal Dice terms); otherwise all terms are equal, so
+    weights tie all the time.  ``noise_deg`` adds random entries over the whole matrix."""
+    rng = np.random.default_rng(seed)
+    rr, cc = [], []
+    for i in range(rows):
+        c = cols - (i % ragged if ragged > 0 else 0)
+        rr.append(np.full(c, row0 + i, dtype=np.int64))
+        cc.append(np.arange(c, dtype=np.int64))
+    if noise_deg > 0:
+        m = int(n * noise_deg)
+        rr.append(rng.integers(0, n, m))
+        cc.append(rng.integers(0, n, m))
+    ptr, ind, _ = coo_to_csr(n, np.concatenate(rr), np.concatenate(cc))
+    val = rng.uniform(-1.0, 1.0, ind.size).astype(np.float32)
+    return ptr, ind, val
+
+
 WORKLOADS = {
     # name: (generator, kwargs, is_symmetric, dense widths for SpMM)
     "zipf65k": (zipf_banded, dict(n=65536, seed=0), False, (32,)),

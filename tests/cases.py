@@ -59,6 +59,21 @@ BIG_CASES = {
     "stencil256": _case(lambda: synth.stencil9(side=256, seed=1), True),
     "rmat14gcn": _case(lambda: synth.rmat_gcn(scale=14, seed=4), True),
     "bigchunk": _case(lambda: synth.rmat(scale=13, seed=9), False, chunk_size=3000),
+    # rows streaming more than 65536 candidates (the heavy-row path of the sketch stage):
+    # equal Dice terms (weights tie all the time), fewer candidates than slots (the sketch
+    # never fills), one cell per lane, unequal terms with noise, a 4096-row chunk, and a
+    # chunk too large for the key tables (element-wise chain)
+    "dense_ties": _case(lambda: synth.dense_block(1024, 0, 300, 300, 21), False, k=16),
+    "dense_fill": _case(lambda: synth.dense_block(2048, 10, 40, 2000, 22), False, k=16),
+    "dense_m32": _case(lambda: synth.dense_block(1024, 0, 200, 400, 23), False, k=8,
+                       oversampling=4.0),
+    "dense_ragged": _case(lambda: synth.dense_block(2048, 100, 300, 320, 24, ragged=50,
+                                                    noise_deg=3.0), False, k=16, chunk_size=512),
+    "dense_c4096": _case(lambda: synth.dense_block(8192, 3000, 300, 300, 25, ragged=7), False,
+                         k=16, chunk_size=4096),
+    "dense_hugechunk": _case(lambda: synth.dense_block(60000, 50000, 280, 300, 26, ragged=3,
+                                                       noise_deg=1.0), False, k=16,
+                             chunk_size=60000),
 }
 
 
