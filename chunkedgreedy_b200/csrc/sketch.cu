@@ -738,6 +738,7 @@ __global__ void __launch_bounds__(S_THREADS, 1) heavy_consume_kernel(SketchArgs 
 // slot code, a key -> slot table over the chunk's rows, and the per-round order.
 constexpr int H_RING = 1024;    // stream elements staged per batch
 constexpr int ROUND_CELLS = 2;  // largest sketch (cells per lane) resolved in rounds
+constexpr int ROUND_RING_BYTES = S_WARPS * 2 * H_RING * 8;
 
 template <int CELLS>
 struct RoundState {
@@ -754,13 +755,13 @@ struct RoundState {
 // One round on a full sketch; returns the number of stream elements resolved (>= 1).
 template <int CELLS>
 __device__ __forceinline__ int round_full(RoundState<CELLS> &st, uint8_t *tab, int32_t cbase,
-                                          const int32_t *bs, const float *ba, int p, int cnt,
-                                          int lane) {
+                                          const int2 *ring, int p, int cnt, int lane) {
   constexpr int M = 32 * CELLS;
   const uint32_t below = (1u << lane) - 1u;
   const bool valid = p + lane < cnt;
-  const int32_t s = valid ? bs[p + lane] : 0;
-  const float al = valid ? ba[p + lane] : 0.0f;
+  const int2 elem = valid ? ring[p + lane] : make_int2(0, 0);
+  const int32_t s = elem.x;
+  const float al = __int_as_float(elem.y);
   uint32_t mine[CELLS];
   int32_t mykey[CELLS];
 #pragma unroll
@@ -808,13 +809,13 @@ __device__ __forceinline__ int round_full(RoundState<CELLS> &st, uint8_t *tab, i
     }
 #pragma unroll
     for (int c = 0; c < CELLS; ++c) pos[c] = -((acc[c][0] + acc[c][1]) + (acc[c][2] + acc[c][3]));
+  }
 #pragma unroll
-    for (int c = 0; c < CELLS; ++c) {
-      st.sw[pos[c]] = mine[c];
-      st.si[pos[c]] = c * 32 + lane;
-      st.sk[pos[c]] = mykey[c];
-      st.rank[c * 32 + lane] = pos[c];
-    }
+  for (int c = 0; c < CELLS; ++c) {
+    st.sw[pos[c]] = mine[c];
+    st.si[pos[c]] = c * 32 + lane;
+    st.sk[pos[c]] = mykey[c];
+    st.rank[c * 32 + lane] = pos[c];
   }
   if (miss) st.miss_pos[mrank] = lane;
   __syncwarp();
@@ -862,13 +863,14 @@ __device__ __forceinline__ int round_full(RoundState<CELLS> &st, uint8_t *tab, i
 // One round while the sketch has empty slots; `filled` is updated.
 template <int CELLS>
 __device__ __forceinline__ int round_fill(RoundState<CELLS> &st, uint8_t *tab, int32_t cbase,
-                                          const int32_t *bs, const float *ba, int p, int cnt,
-                                          int lane, int &filled) {
+                                          const int2 *ring, int p, int cnt, int lane,
+                                          int &filled) {
   constexpr int M = 32 * CELLS;
   const uint32_t below = (1u << lane) - 1u;
   const bool valid = p + lane < cnt;
-  const int32_t s = valid ? bs[p + lane] : 0;
-  const float al = valid ? ba[p + lane] : 0.0f;
+  const int2 elem = valid ? ring[p + lane] : make_int2(0, 0);
+  const int32_t s = elem.x;
+  const float al = __int_as_float(elem.y);
   const int q = valid ? static_cast<int>(tab[s - cbase]) - 1 : 0;
   const bool miss = valid && q < 0;
   const bool hit = valid && q >= 0;
@@ -900,20 +902,28 @@ __device__ __forceinline__ int round_fill(RoundState<CELLS> &st, uint8_t *tab, i
 // Same contract as heavy_consume_kernel (one warp per heavy row, one block per SM, final
 // sketch to heavy_state), resolving the stream in rounds.  The dynamic shared memory that
 // keeps the block alone on its SM holds the key -> slot tables, `tab_bytes` per warp.
+// copies `cnt` stream elements into a ring buffer without passing through registers
+__device__ __forceinline__ void stage_batch(int2 *ring, const int2 *in, int cnt, int lane) {
+  for (int i = lane; i < cnt; i += 32) {
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(ring + i));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(in + i) : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
 template <int CELLS>
 __global__ void __launch_bounds__(S_THREADS, 1) heavy_rounds_kernel(SketchArgs a, int tab_bytes) {
+  // dynamic shared memory: two stream buffers per warp (the next batch lands while this
+  // one is consumed), then the key tables
   extern __shared__ __align__(16) unsigned char heavy_dyn[];
-  __shared__ int32_t ring_s[S_WARPS][H_RING];
-  __shared__ float ring_a[S_WARPS][H_RING];
+  int2(*rings)[2][H_RING] = reinterpret_cast<int2(*)[2][H_RING]>(heavy_dyn);
   __shared__ RoundState<CELLS> state[S_WARPS];
   constexpr int M = 32 * CELLS;
   const int lane = lane_id(), warp = threadIdx.x >> 5;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t heavy = a.ctrl[CTRL_HEAVY_ROWS];
-  int32_t *bs = ring_s[warp];
-  float *ba = ring_a[warp];
   RoundState<CELLS> &st = state[warp];
-  uint8_t *tab = heavy_dyn + static_cast<size_t>(warp) * tab_bytes;
+  uint8_t *tab = heavy_dyn + ROUND_RING_BYTES + static_cast<size_t>(warp) * tab_bytes;
   for (int i = lane * 16; i < tab_bytes; i += 32 * 16) *reinterpret_cast<uint4 *>(tab + i) = make_uint4(0, 0, 0, 0);
   for (;;) {
     uint32_t item = 0;
@@ -929,20 +939,25 @@ __global__ void __launch_bounds__(S_THREADS, 1) heavy_rounds_kernel(SketchArgs a
       st.key[c * 32 + lane] = -1;
       st.w[c * 32 + lane] = 0u;
     }
-    int filled = 0;
+    int filled = 0, buf = 0;
     __syncwarp();
+    stage_batch(rings[warp][0], in, static_cast<int>(total < H_RING ? total : H_RING), lane);
     for (uint32_t base = 0; base < total; base += H_RING) {
       const int cnt = static_cast<int>(total - base < H_RING ? total - base : H_RING);
-      for (int i = lane; i < cnt; i += 32) {
-        const int2 e = in[base + i];
-        bs[i] = e.x;
-        ba[i] = __int_as_float(e.y);
-      }
+      const uint32_t next = base + H_RING;
+      if (next < total)
+        stage_batch(rings[warp][buf ^ 1], in + next, static_cast<int>(total - next < H_RING ? total - next : H_RING), lane);
+      else
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 1;" ::: "memory");  // all but the newest group: this batch is in
       __syncwarp();
+      const int2 *ring = rings[warp][buf];
       int p = 0;
-      while (p < cnt && filled < M) p += round_fill<CELLS>(st, tab, cbase, bs, ba, p, cnt, lane, filled);
-      while (p < cnt) p += round_full<CELLS>(st, tab, cbase, bs, ba, p, cnt, lane);
+      while (p < cnt && filled < M) p += round_fill<CELLS>(st, tab, cbase, ring, p, cnt, lane, filled);
+      while (p < cnt) p += round_full<CELLS>(st, tab, cbase, ring, p, cnt, lane);
+      buf ^= 1;
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     int32_t *out = a.heavy_state + static_cast<size_t>(item) * (2 * CELLS * 32);
 #pragma unroll
     for (int c = 0; c < CELLS; ++c) {
@@ -994,7 +1009,7 @@ bool launch_cells(Context &ctx, const SketchArgs &a) {
     CSG_CUDA(cudaFuncGetAttributes(&fa, heavy_rounds_kernel<CELLS>));
     const int pad = ctx.smem_optin - 1024 - static_cast<int>(fa.sharedSizeBytes);
     const int64_t tab_bytes = (static_cast<int64_t>(a.chunk) + 15) / 16 * 16;
-    if (tab_bytes * S_WARPS <= pad) {
+    if (ROUND_RING_BYTES + tab_bytes * S_WARPS <= pad) {
       CSG_CUDA(cudaFuncSetAttribute(heavy_rounds_kernel<CELLS>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, pad));
       heavy_rounds_kernel<CELLS><<<ctx.num_sms, S_THREADS, pad, ctx.stream>>>(a, static_cast<int>(tab_bytes));
