@@ -733,7 +733,7 @@ __global__ void __launch_bounds__(S_THREADS, 1) heavy_consume_kernel(SketchArgs 
 // rewrites slot E_i, hits add their alpha (hits on one key all add the same alpha, so
 // their order is immaterial), and the next round starts L elements further on.  While the
 // sketch still has empty slots only (1) applies and miss number i fills the next i-th slot.
-// On the longest R-MAT rows a round resolves 16 elements on average in about 1200 cycles,
+// On the longest R-MAT rows a round resolves 16 elements on average in about 1000 cycles,
 // where 16 sequential steps take 2200.  State lives in shared memory: weights and keys by
 // slot code, a key -> slot table over the chunk's rows, and the per-round order.
 constexpr int H_RING = 1024;    // stream elements staged per batch
@@ -750,14 +750,27 @@ struct RoundState {
   int32_t rank[M];               // position of each slot in that order
   int32_t sk[M];                 // ... and keys
   int32_t miss_pos[32];          // lane of the i-th miss of the window
+  uint32_t fence_sink;           // see phase_fence
 };
+
+// Keeps the phases of a round apart in the instruction schedule.  Left alone, ptxas
+// interleaves the window look-up, the count and the limit look-ups, and the round takes
+// 1220 cycles; with a read of %clock between them (which it does not move code across, as
+// long as the value is used) it takes 995.  The values go to a word nobody reads.
+__device__ __forceinline__ void phase_fence(uint32_t &sink) {
+  uint32_t t;
+  asm volatile("mov.u32 %0, %%clock;" : "=r"(t));
+  sink ^= t;
+}
 
 // One round on a full sketch; returns the number of stream elements resolved (>= 1).
 template <int CELLS>
 __device__ __forceinline__ int round_full(RoundState<CELLS> &st, uint8_t *tab, int32_t cbase,
-                                          const int2 *ring, int p, int cnt, int lane) {
+                                          const int2 *ring, int p, int cnt, int lane,
+                                          uint32_t &sink) {
   constexpr int M = 32 * CELLS;
   const uint32_t below = (1u << lane) - 1u;
+  phase_fence(sink);
   const bool valid = p + lane < cnt;
   const int2 elem = valid ? ring[p + lane] : make_int2(0, 0);
   const int32_t s = elem.x;
@@ -779,6 +792,7 @@ __device__ __forceinline__ int round_full(RoundState<CELLS> &st, uint8_t *tab, i
   const uint32_t missing = __ballot_sync(FULL, miss);
   const int mtot = __popc(missing);
   const int mrank = __popc(missing & below);
+  phase_fence(sink);
   // Position of this lane's slots in the (weight, code) order of S0: the number of entries
   // (x, i) below (mine, code).  Weight bit patterns are below 2^31, so x < y is the sign of
   // x - y, and "below" is x < mine + 1 for a smaller code i, x < mine for a larger one.
@@ -817,8 +831,10 @@ __device__ __forceinline__ int round_full(RoundState<CELLS> &st, uint8_t *tab, i
     st.sk[pos[c]] = mykey[c];
     st.rank[c * 32 + lane] = pos[c];
   }
+  phase_fence(sink);
   if (miss) st.miss_pos[mrank] = lane;
   __syncwarp();
+  phase_fence(sink);
   // every lane reads what either kind of element needs, then selects
   const int rho = st.rank[hit ? q : 0];
   const int tgt = st.si[mrank];
@@ -840,6 +856,7 @@ __device__ __forceinline__ int round_full(RoundState<CELLS> &st, uint8_t *tab, i
     if (nb <= top) lim = nb > base ? (mrank + 1 < mtot ? at_next : 32) : lane;
     if (same & below) lim = lane;  // (1)
   }
+  phase_fence(sink);
   int L = static_cast<int>(__reduce_min_sync(FULL, static_cast<uint32_t>(lim)));
   L = L < 1 ? 1 : L;  // one element alone is always resolved exactly
   const bool applies = lane < L;
@@ -911,6 +928,51 @@ __device__ __forceinline__ void stage_batch(int2 *ring, const int2 *in, int cnt,
   asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
+// One heavy row, start to finish: stream batches in, rounds, final sketch out.  Not
+// inlined: compiled as part of the kernel's ticket loop the same rounds take 1280 cycles
+// instead of 1000.
+template <int CELLS>
+__device__ __noinline__ void rounds_row(const int2 *in, uint32_t total, int32_t cbase,
+                                        RoundState<CELLS> &st, uint8_t *tab, int2 *ring0, int2 *ring1,
+                                        int32_t *out) {
+  constexpr int M = 32 * CELLS;
+  const int lane = lane_id();
+#pragma unroll
+  for (int c = 0; c < CELLS; ++c) {
+    st.key[c * 32 + lane] = -1;
+    st.w[c * 32 + lane] = 0u;
+  }
+  int filled = 0, buf = 0;
+  uint32_t sink = 0;
+  __syncwarp();
+  stage_batch(ring0, in, static_cast<int>(total < H_RING ? total : H_RING), lane);
+  for (uint32_t base = 0; base < total; base += H_RING) {
+    const int cnt = static_cast<int>(total - base < H_RING ? total - base : H_RING);
+    const uint32_t next = base + H_RING;
+    if (next < total)
+      stage_batch(buf ? ring0 : ring1, in + next, static_cast<int>(total - next < H_RING ? total - next : H_RING), lane);
+    else
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");  // all but the newest group: this batch is in
+    __syncwarp();
+    const int2 *ring = buf ? ring1 : ring0;
+    int p = 0;
+    while (p < cnt && filled < M) p += round_fill<CELLS>(st, tab, cbase, ring, p, cnt, lane, filled);
+    while (p < cnt) p += round_full<CELLS>(st, tab, cbase, ring, p, cnt, lane, sink);
+    buf ^= 1;
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+  for (int c = 0; c < CELLS; ++c) {
+    const int32_t kk = st.key[c * 32 + lane];
+    out[(2 * c) * 32 + lane] = kk;
+    out[(2 * c + 1) * 32 + lane] = static_cast<int32_t>(st.w[c * 32 + lane]);
+    if (kk >= 0) tab[kk - cbase] = 0;  // the table is empty again for the next row
+  }
+  if (lane == 0) st.fence_sink = sink;
+  __syncwarp();
+}
+
 template <int CELLS>
 __global__ void __launch_bounds__(S_THREADS, 1) heavy_rounds_kernel(SketchArgs a, int tab_bytes) {
   // dynamic shared memory: two stream buffers per warp (the next batch lands while this
@@ -918,11 +980,9 @@ __global__ void __launch_bounds__(S_THREADS, 1) heavy_rounds_kernel(SketchArgs a
   extern __shared__ __align__(16) unsigned char heavy_dyn[];
   int2(*rings)[2][H_RING] = reinterpret_cast<int2(*)[2][H_RING]>(heavy_dyn);
   __shared__ RoundState<CELLS> state[S_WARPS];
-  constexpr int M = 32 * CELLS;
   const int lane = lane_id(), warp = threadIdx.x >> 5;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t heavy = a.ctrl[CTRL_HEAVY_ROWS];
-  RoundState<CELLS> &st = state[warp];
   uint8_t *tab = heavy_dyn + ROUND_RING_BYTES + static_cast<size_t>(warp) * tab_bytes;
   for (int i = lane * 16; i < tab_bytes; i += 32 * 16) *reinterpret_cast<uint4 *>(tab + i) = make_uint4(0, 0, 0, 0);
   for (;;) {
@@ -931,42 +991,9 @@ __global__ void __launch_bounds__(S_THREADS, 1) heavy_rounds_kernel(SketchArgs a
     item = __shfl_sync(FULL, item, 0);
     if (item >= heavy) break;
     const int32_t r = a.row_list[item];
-    const uint32_t total = a.row_work[r];
-    const int32_t cbase = (r / a.chunk) * a.chunk;
-    const int2 *in = a.hstream + a.heavy_off[item];
-#pragma unroll
-    for (int c = 0; c < CELLS; ++c) {
-      st.key[c * 32 + lane] = -1;
-      st.w[c * 32 + lane] = 0u;
-    }
-    int filled = 0, buf = 0;
-    __syncwarp();
-    stage_batch(rings[warp][0], in, static_cast<int>(total < H_RING ? total : H_RING), lane);
-    for (uint32_t base = 0; base < total; base += H_RING) {
-      const int cnt = static_cast<int>(total - base < H_RING ? total - base : H_RING);
-      const uint32_t next = base + H_RING;
-      if (next < total)
-        stage_batch(rings[warp][buf ^ 1], in + next, static_cast<int>(total - next < H_RING ? total - next : H_RING), lane);
-      else
-        asm volatile("cp.async.commit_group;" ::: "memory");
-      asm volatile("cp.async.wait_group 1;" ::: "memory");  // all but the newest group: this batch is in
-      __syncwarp();
-      const int2 *ring = rings[warp][buf];
-      int p = 0;
-      while (p < cnt && filled < M) p += round_fill<CELLS>(st, tab, cbase, ring, p, cnt, lane, filled);
-      while (p < cnt) p += round_full<CELLS>(st, tab, cbase, ring, p, cnt, lane);
-      buf ^= 1;
-    }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    int32_t *out = a.heavy_state + static_cast<size_t>(item) * (2 * CELLS * 32);
-#pragma unroll
-    for (int c = 0; c < CELLS; ++c) {
-      const int32_t kk = st.key[c * 32 + lane];
-      out[(2 * c) * 32 + lane] = kk;
-      out[(2 * c + 1) * 32 + lane] = static_cast<int32_t>(st.w[c * 32 + lane]);
-      if (kk >= 0) tab[kk - cbase] = 0;  // the table is empty again for the next row
-    }
-    __syncwarp();
+    rounds_row<CELLS>(a.hstream + a.heavy_off[item], a.row_work[r], (r / a.chunk) * a.chunk, state[warp],
+                      tab, rings[warp][0], rings[warp][1],
+                      a.heavy_state + static_cast<size_t>(item) * (2 * CELLS * 32));
   }
 }
 
