@@ -351,7 +351,7 @@ def run_ours(args, rank, world, local_rank):
         "clocks": clocks.summary(),
         "stages_ms": stage,
         "roofline": {"bound": "hbm",
-                     "kernel": "sketch + top-k stage (heavy_expand, heavy_consume, sketch_kernel)",
+                     "kernel": "sketch + top-k stage (heavy_expand, heavy_rounds, sketch_kernel)",
                      "achieved": ach,
                      "peak": hbm, "unit": "GB/s", "frac": ach / hbm, "peak_source": peak_src,
                      "algorithmic_bytes": int(b_sketch),
