@@ -225,7 +225,7 @@ def run_reference(args, rank, world):
         "note": "the reference implements csg only in CUDA; this arm is the OpenMP restatement "
                 "of its arithmetic (oracle/csg_oracle.c) on the host cores",
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def workload_config(n, nnz, k, args):
@@ -374,7 +374,7 @@ def run_ours(args, rank, world, local_rank):
     if world == 1 and args.gcn:
         line["gcn"] = gcn_section(d_ptr, d_ind, torch.from_numpy(val).to(dev), n, ctx,
                                   args.gcn_epochs)
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # DRAM bytes (read + write) of the sketch stage's kernels per csg call, from an ncu capture
@@ -445,7 +445,25 @@ def gcn_section(d_ptr, d_ind, d_val, n, ctx, epochs):
     return r
 
 
+_JSON_OUT = None
+
+
+def emit(line):
+    """The one JSON line, on the process's original stdout."""
+    out = _JSON_OUT if _JSON_OUT is not None else sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
+
+
 def main():
+    # Libraries write to stdout too (NCCL prints its version there at any NCCL_DEBUG level
+    # the launcher may have set).  Stdout has to carry the JSON line and nothing else, so
+    # file descriptor 1 is pointed at stderr for the whole run and the line goes to a
+    # duplicate of the original descriptor.
+    global _JSON_OUT
+    sys.stdout.flush()
+    _JSON_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
@@ -472,9 +490,6 @@ def main():
         run_reference(args, rank, world)
         return
     if world > 1:
-        # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; stdout carries the JSON line only
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
