@@ -33,7 +33,7 @@
 //    kernel of all other rows follows as a programmatic dependent launch: it starts as
 //    soon as the chain kernel's blocks are running and fills the SMs that kernel leaves or
 //    frees;
-//  * for sketches of up to 64 slots the chain kernel does not step through the stream one
+//  * for sketches of up to 128 slots the chain kernel does not step through the stream one
 //    element at a time: it resolves the longest prefix of the next 32 elements whose
 //    outcome can be read off the sketch as it stands, all lanes at once (see "the chains
 //    in rounds" below) - 16 elements per round on the longest R-MAT rows, at under half
@@ -737,7 +737,7 @@ __global__ void __launch_bounds__(S_THREADS, 1) heavy_consume_kernel(SketchArgs 
 // where 16 sequential steps take 2200.  State lives in shared memory: weights and keys by
 // slot code, a key -> slot table over the chunk's rows, and the per-round order.
 constexpr int H_RING = 1024;    // stream elements staged per batch
-constexpr int ROUND_CELLS = 2;  // largest sketch (cells per lane) resolved in rounds
+constexpr int ROUND_CELLS = 4;  // largest sketch (cells per lane) resolved in rounds
 constexpr int ROUND_RING_BYTES = S_WARPS * 2 * H_RING * 8;
 
 template <int CELLS>

@@ -71,6 +71,12 @@ BIG_CASES = {
                                                     noise_deg=3.0), False, k=16, chunk_size=512),
     "dense_c4096": _case(lambda: synth.dense_block(8192, 3000, 300, 300, 25, ragged=7), False,
                          k=16, chunk_size=4096),
+    # three and four cells per lane on the heavy-row path
+    "dense_m96": _case(lambda: synth.dense_block(1024, 0, 300, 300, 27, ragged=11), False, k=24,
+                       oversampling=3.5),
+    "dense_m128": _case(lambda: synth.dense_block(2048, 64, 320, 330, 28, ragged=40,
+                                                  noise_deg=2.0), False, k=30),
+    "dense_m128_ties": _case(lambda: synth.dense_block(1024, 0, 300, 300, 29), False, k=32),
     "dense_hugechunk": _case(lambda: synth.dense_block(60000, 50000, 280, 300, 26, ragged=3,
                                                        noise_deg=1.0), False, k=16,
                              chunk_size=60000),

@@ -54,7 +54,8 @@ def test_csg_larger_cases_against_oracle(name):
 
 
 @pytest.mark.parametrize("name", ["hubsym", "rmat12", "m512", "bigchunk", "rmat16", "dense_ties",
-                                  "dense_fill", "dense_m32", "dense_ragged"])
+                                  "dense_fill", "dense_m32", "dense_ragged", "dense_m96",
+                                  "dense_m128", "dense_m128_ties"])
 def test_csg_against_reference_library(name):
     from oracle import ref
     if not ref.available():
