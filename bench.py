@@ -271,6 +271,9 @@ def run_ours(args, rank, world, local_rank):
     h_out = torch.empty(n, dtype=torch.int32).pin_memory()
 
     def step_e2e():
+        if world == 1:  # the C ABI's host-buffer entry point: copies in, reorder, copy out
+            sp.chunk_similarity_greedy_host(h_ptr, h_ind, k=k, chunk_size=CHUNK, out=h_out, ctx=ctx)
+            return
         dp = h_ptr.to(dev, non_blocking=True)
         di = h_ind.to(dev, non_blocking=True)
         local = csgdist.csg_shard(dp, di, n, r0, k=k, chunk_size=CHUNK, ctx=ctx)

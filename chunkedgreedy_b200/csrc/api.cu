@@ -258,6 +258,7 @@ void sporder_context_destroy(sporder_context_t h) {
   cudaSetDevice(c.device);
   cudaStreamSynchronize(c.stream);
   if (c.ws) cudaFree(c.ws);
+  if (c.stage) cudaFree(c.stage);
   for (auto &ev : c.ev)
     if (ev) cudaEventDestroy(ev);
   if (c.h_pinned) cudaFreeHost(c.h_pinned);
@@ -345,11 +346,23 @@ int32_t sporder_chunk_similarity_greedy_host(sporder_context_t ctx, int32_t n, i
   csg::Context &c = ctx->c;
   auto run = [&]() -> bool {
     CSG_CUDA(cudaSetDevice(c.device));
-    // staging buffers of the host entry point live outside the workspace cache
-    int32_t *d_ptr = nullptr, *d_ind = nullptr, *d_order = nullptr;
-    CSG_CUDA(cudaMallocAsync(&d_ptr, sizeof(int32_t) * (static_cast<size_t>(n) + 1), c.stream));
-    CSG_CUDA(cudaMallocAsync(&d_ind, sizeof(int32_t) * static_cast<size_t>(nnz > 0 ? nnz : 1), c.stream));
-    CSG_CUDA(cudaMallocAsync(&d_order, sizeof(int32_t) * static_cast<size_t>(n), c.stream));
+    // Device copies of the inputs and the result live in a buffer of the context that only
+    // grows: a stream-ordered allocation per call went back to the driver at every
+    // synchronisation and cost more than the reorder itself.
+    const size_t b_ptr = (sizeof(int32_t) * (static_cast<size_t>(n) + 1) + 255) & ~size_t(255);
+    const size_t b_ind = (sizeof(int32_t) * static_cast<size_t>(nnz > 0 ? nnz : 1) + 255) & ~size_t(255);
+    const size_t b_ord = sizeof(int32_t) * static_cast<size_t>(n);
+    if (b_ptr + b_ind + b_ord > c.stage_bytes) {
+      CSG_CUDA(cudaStreamSynchronize(c.stream));
+      if (c.stage) CSG_CUDA(cudaFree(c.stage));
+      c.stage = nullptr;
+      c.stage_bytes = 0;
+      CSG_CUDA(cudaMalloc(&c.stage, b_ptr + b_ind + b_ord));
+      c.stage_bytes = b_ptr + b_ind + b_ord;
+    }
+    int32_t *d_ptr = reinterpret_cast<int32_t *>(c.stage);
+    int32_t *d_ind = reinterpret_cast<int32_t *>(c.stage + b_ptr);
+    int32_t *d_order = reinterpret_cast<int32_t *>(c.stage + b_ptr + b_ind);
     CSG_CUDA(cudaMemcpyAsync(d_ptr, h_ptr, sizeof(int32_t) * (static_cast<size_t>(n) + 1),
                              cudaMemcpyHostToDevice, c.stream));
     if (nnz > 0)
@@ -360,9 +373,6 @@ int32_t sporder_chunk_similarity_greedy_host(sporder_context_t ctx, int32_t n, i
     if (ok)
       CSG_CUDA(cudaMemcpyAsync(h_new_order, d_order, sizeof(int32_t) * static_cast<size_t>(n),
                                cudaMemcpyDeviceToHost, c.stream));
-    cudaFreeAsync(d_ptr, c.stream);
-    cudaFreeAsync(d_ind, c.stream);
-    cudaFreeAsync(d_order, c.stream);
     CSG_CUDA(cudaStreamSynchronize(c.stream));
     return ok;
   };

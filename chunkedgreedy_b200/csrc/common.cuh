@@ -50,6 +50,8 @@ struct Context {
   size_t ws_bytes = 0;
   cudaEvent_t ev[8] = {};
   int *h_pinned = nullptr;  // small pinned host buffer for counters (64 ints)
+  char *stage = nullptr;    // device copies of host inputs (host-buffer entry point), kept between calls
+  size_t stage_bytes = 0;
 };
 
 bool ensure_workspace(Context &ctx, size_t bytes);

@@ -244,6 +244,15 @@ def dense_block(n, row0, rows, cols, seed, ragged=0, noise_deg=0.0):
     return ptr, ind, val
 
 
+def rotate_labels(ptr, ind, val, shift):
+    """The same pattern with row and column r renamed (r + shift) mod n: moves the hub rows of
+    an R-MAT matrix away from chunk 0."""
+    n = ptr.size - 1
+    rows = np.repeat(np.arange(n, dtype=np.int64), np.diff(ptr))
+    ptr2, ind2, order = coo_to_csr(n, (rows + shift) % n, (ind.astype(np.int64) + shift) % n)
+    return ptr2, ind2, val
+
+
 WORKLOADS = {
     # name: (generator, kwargs, is_symmetric, dense widths for SpMM)
     "zipf65k": (zipf_banded, dict(n=65536, seed=0), False, (32,)),

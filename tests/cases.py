@@ -77,6 +77,9 @@ BIG_CASES = {
     "dense_m128": _case(lambda: synth.dense_block(2048, 64, 320, 330, 28, ragged=40,
                                                   noise_deg=2.0), False, k=30),
     "dense_m128_ties": _case(lambda: synth.dense_block(1024, 0, 300, 300, 29), False, k=32),
+    # hub rows in the middle of the matrix
+    "rmat15_rotated": _case(lambda: synth.rotate_labels(*synth.rmat(scale=15, seed=5), 10240 + 77),
+                            False, chunk_size=512),
     "dense_hugechunk": _case(lambda: synth.dense_block(60000, 50000, 280, 300, 26, ragged=3,
                                                        noise_deg=1.0), False, k=16,
                              chunk_size=60000),
