@@ -123,7 +123,7 @@ bool plan_scratch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, uint
   const size_t hmax = cap / (size_t(1) << (SKETCH_HEAVY_BUCKET - 1)) + 1;
   const size_t o_hs = ar.take(8 * cap), o_ho = ar.take(4 * (hmax + 1));
   const size_t o_hst = ar.take(4 * hmax * 2 * (p.M / 32) * 32);
-  const size_t pmax = z / 2048 + hmax + 1;  // slices of 2048 columns
+  const size_t pmax = z / SKETCH_PART_COLS + hmax + 1;  // column slices of the heavy rows
   const size_t o_pb = ar.take(4 * (hmax + 2)), o_po = ar.take(4 * (pmax + 1));
   const size_t o_table = user_table ? 0 : ar.take(8 * static_cast<size_t>(n) * p.k);
   if (!ensure_workspace(ctx, ar.off)) return false;

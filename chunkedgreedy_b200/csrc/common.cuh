@@ -116,6 +116,7 @@ enum {
   CTRL_WORDS = 168
 };
 
+constexpr int SKETCH_PART_COLS = 128;   // columns of a heavy row whose stream one warp writes out
 constexpr int SKETCH_HEAVY_BUCKET = 17;  // rows streaming >= 65536 candidates are "heavy"
 
 // stage launchers; all enqueue on ctx.stream and return false after set_error()

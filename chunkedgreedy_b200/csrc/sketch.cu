@@ -27,7 +27,7 @@
 //  * the rows with the longest streams set the run time of the whole call, and a warp
 //    that shares its scheduler with seven others takes 1.6x longer per step.  Those rows
 //    (65536 stream elements or more) take a path of their own: their streams are written
-//    out to memory by the whole grid (heavy_expand_kernel, one warp per 2048 columns),
+//    out to memory by the whole grid (heavy_expand_kernel, one warp per 128 columns),
 //    then a chain kernel runs one warp per row and one warp per scheduler - one block per
 //    SM, kept alone there by its shared-memory request - doing nothing but consuming.  The
 //    kernel of all other rows follows as a programmatic dependent launch: it starts as
@@ -48,7 +48,9 @@ namespace {
 constexpr int S_WARPS = 4;
 constexpr int S_THREADS = 32 * S_WARPS;
 constexpr int S_RING = 256;    // stream elements per batch, light rows
-constexpr int H_PART = 2048;   // columns of a heavy row expanded by one warp
+constexpr int H_PART = SKETCH_PART_COLS;  // columns of a heavy row expanded by one warp: small enough
+                                         // that a slice of hub columns (up to chunk-1 candidates
+                                         // each) does not become the last warp to finish
 constexpr int S_LONG = 48;     // groups with at least this many pending entries are copied by the whole warp
 
 struct SketchArgs {
@@ -540,7 +542,9 @@ __global__ void __launch_bounds__(1024) heavy_offsets_kernel(SketchArgs a) {
       const unsigned long long e_off = excl & ((1ull << 43) - 1);
       a.heavy_off[i] = static_cast<uint32_t>(e_off > 0xFFFFFFFFull ? 0xFFFFFFFFull : e_off);
       a.part_base[i] = static_cast<uint32_t>(excl >> 43);
-      if (e_off + v > a.stream_cap) atomicMin(&count_s, i);  // first row that does not fit
+      // first row that does not fit the stream buffer, or whose slices would overflow the
+      // 21 bits the scan has for their count: it and the rows behind it stay with the light rows
+      if (e_off + v > a.stream_cap || (excl >> 43) + np >= (1ull << 21)) atomicMin(&count_s, i);
     }
     __syncthreads();
     if (threadIdx.x == 0) carry_s = carry + tot;

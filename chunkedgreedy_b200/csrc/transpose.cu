@@ -480,8 +480,16 @@ __global__ void __launch_bounds__(T_THREADS) heavy_scatter_kernel(TransposeArgs 
 
 // Group of every sorted element by two bounded binary searches: a column group
 // has at most one entry per row of the chunk, so its ends lie within `rows`
-// positions of the element.
+// positions of the element.  For chunks of up to E_ROWS rows the searches run on
+// shared-memory copies - the tile's keys with a halo of rows-1 on either side and the
+// chunk's row pointers - and the rows' work counters are summed in shared memory first:
+// on global memory the kernel was bound by the latency of some thirty dependent loads per
+// element and by atomics of a whole tile landing on the same few hub rows.
+constexpr int E_ROWS = 1024;
 __global__ void __launch_bounds__(T_THREADS) heavy_emit_kernel(TransposeArgs a) {
+  __shared__ uint32_t skey[T_TILE + 2 * (E_ROWS - 1)];
+  __shared__ int32_t sptr[E_ROWS + 1];
+  __shared__ uint32_t swork[E_ROWS];
   const int32_t TT = static_cast<int32_t>(a.ctrl[CTRL_HEAVY_TILES]);
   const int32_t H = static_cast<int32_t>(a.ctrl[CTRL_HEAVY_COUNT]);
   const int f = (a.passes - 1) & 1;
@@ -489,13 +497,23 @@ __global__ void __launch_bounds__(T_THREADS) heavy_emit_kernel(TransposeArgs a) 
     const TileRef r = tile_ref(a, t, H);
     const uint32_t *K = (f ? a.keyB : a.keyA) + r.b;
     const uint32_t *P = (f ? a.payB : a.payA) + r.b;
+    const bool staged = r.rows <= E_ROWS;
+    int32_t w0 = 0;  // first sorted position held in skey
+    if (staged) {
+      w0 = r.off - (r.rows - 1) < 0 ? 0 : r.off - (r.rows - 1);
+      const int32_t w1 = r.off + r.cnt + (r.rows - 1) < r.L ? r.off + r.cnt + (r.rows - 1) : r.L;
+      for (int32_t j = threadIdx.x; j < w1 - w0; j += T_THREADS) skey[j] = K[w0 + j];
+      for (int32_t j = threadIdx.x; j <= r.rows; j += T_THREADS) sptr[j] = a.ptr[r.cs + j];
+      for (int32_t j = threadIdx.x; j < r.rows; j += T_THREADS) swork[j] = 0u;
+      __syncthreads();
+    }
     for (int li = threadIdx.x; li < r.cnt; li += T_THREADS) {
       const int32_t i = r.off + li;
-      const uint32_t key = K[i];
+      const uint32_t key = staged ? skey[i - w0] : K[i];
       int32_t lo = i - (r.rows - 1) < 0 ? 0 : i - (r.rows - 1), hi = i;  // first index with K >= key
       while (lo < hi) {
         const int32_t mid = (lo + hi) >> 1;
-        if (K[mid] < key)
+        if ((staged ? skey[mid - w0] : K[mid]) < key)
           lo = mid + 1;
         else
           hi = mid;
@@ -505,18 +523,33 @@ __global__ void __launch_bounds__(T_THREADS) heavy_emit_kernel(TransposeArgs a) 
       hi = i + r.rows < r.L ? i + r.rows : r.L;  // first index with K > key
       while (lo < hi) {
         const int32_t mid = (lo + hi) >> 1;
-        if (K[mid] <= key)
+        if ((staged ? skey[mid - w0] : K[mid]) <= key)
           lo = mid + 1;
         else
           hi = mid;
       }
       const int32_t len = lo - st;
       const int32_t p = static_cast<int32_t>(P[i]);
-      const int32_t row = row_of(a.ptr, r.cs, r.cs + r.rows, r.b + p);
-      a.cand[r.b + i] = make_int2(row, a.ptr[row + 1] - a.ptr[row]);
+      int32_t row, rl;
+      if (staged) {
+        const int32_t lr = row_of(sptr, 0, r.rows, r.b + p);
+        row = r.cs + lr;
+        rl = sptr[lr + 1] - sptr[lr];
+        if (len >= 2) atomicAdd(&swork[lr], static_cast<uint32_t>(len - 1));
+      } else {
+        row = row_of(a.ptr, r.cs, r.cs + r.rows, r.b + p);
+        rl = a.ptr[row + 1] - a.ptr[row];
+        if (len >= 2) atomicAdd(&a.row_work[row], static_cast<uint32_t>(len - 1));
+      }
+      a.cand[r.b + i] = make_int2(row, rl);
       a.seg[r.b + p] = make_int2(r.b + st, len);
       a.seg_rank[r.b + p] = i - st;
-      if (len >= 2) atomicAdd(&a.row_work[row], static_cast<uint32_t>(len - 1));
+    }
+    if (staged) {
+      __syncthreads();
+      for (int32_t j = threadIdx.x; j < r.rows; j += T_THREADS)
+        if (swork[j]) atomicAdd(&a.row_work[r.cs + j], swork[j]);
+      __syncthreads();
     }
   }
 }
