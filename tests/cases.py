@@ -76,6 +76,8 @@ BIG_CASES = {
                        oversampling=3.5),
     "dense_m128": _case(lambda: synth.dense_block(2048, 64, 320, 330, 28, ragged=40,
                                                   noise_deg=2.0), False, k=30),
+    # eight cells per lane: beyond the sketches resolved in rounds (element-wise chain)
+    "dense_m256": _case(lambda: synth.dense_block(1024, 0, 300, 300, 30, ragged=13), False, k=64),
     "dense_m128_ties": _case(lambda: synth.dense_block(1024, 0, 300, 300, 29), False, k=32),
     # hub rows in the middle of the matrix
     "rmat15_rotated": _case(lambda: synth.rotate_labels(*synth.rmat(scale=15, seed=5), 10240 + 77),
