@@ -19,7 +19,7 @@ import ctypes as C
 from . import _lib
 
 __all__ = ["Context", "chunk_similarity_greedy", "reorder", "spmm", "csg_table",
-           "chunk_similarity_greedy_host", "kernel_launches"]
+           "chunk_similarity_greedy_host", "kernel_launches", "count_pillars"]
 
 _default_ctx = {}
 
@@ -198,6 +198,26 @@ def chunk_similarity_greedy_host(ptr, ind, *, is_symmetric=False, k=0, oversampl
     if rc != 0:
         _lib.check()
     return out
+
+
+def count_pillars(ptr, ind, height, *, ctx=None):
+    """Distinct (row // height, column) pairs of a CSR pattern: the reference's reordering
+    quality metric, fewer is better (sporder/python/sporder/__init__.py:152-172)."""
+    torch = _torch()
+    ptr = _as_tensor(ptr, torch.int32, "ptr")
+    ind = _as_tensor(ind, torch.int32, "ind")
+    n, nnz = _sizes(ptr, ind)
+    if int(height) < 1:
+        raise ValueError("height must be >= 1")
+    ctx = _ctx(ctx)
+    lib = _lib.load()
+    out = C.c_int32(0)
+    with torch.cuda.device(ptr.device):
+        _enter(ctx, ptr)
+        lib.sporder_count_pillars(ctx.handle, n, nnz, ptr.data_ptr(), ind.data_ptr(), int(height),
+                                  C.byref(out))
+    _lib.check()
+    return int(out.value)
 
 
 def reorder(ptr, ind, new_order, *, val=None, symmetric=False, ctx=None):

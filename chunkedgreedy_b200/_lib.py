@@ -52,6 +52,8 @@ SYMBOLS = {
     "sporder_spmm_async": (C.c_int32, [_P, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P]),
     "sporder_spmm_static": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P]),
     "sporder_kernel_launches": (C.c_uint64, []),
+    "sporder_count_pillars": (None, [_P, C.c_int32, C.c_int32, _P, _P, C.c_int32,
+                                     C.POINTER(C.c_int32)]),
 }
 
 

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libsporder_b200.so")
-SOURCES = ["api.cu", "transpose.cu", "sketch.cu", "greedy.cu", "reorder.cu", "spmm.cu"]
+SOURCES = ["api.cu", "transpose.cu", "sketch.cu", "greedy.cu", "reorder.cu", "spmm.cu", "pillars.cu"]
 # No fast-math: the Dice terms need the IEEE fp32 divide and plain fp32 adds.
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr"]

@@ -71,6 +71,17 @@ SPORDER_API void sporder_chunk_similarity_greedy(
     bool is_symmetric, int32_t k, float oversampling, int32_t chunk_size, int32_t *d_new_order,
     sporder_csg_timing_t *timing, sporder_csg_stats_t *stats);
 
+/* replaces sporder/include/sporder.h:276-279 (sporder/src/count_pillars.cu:38-85):
+ * *count = number of distinct (row / height, column) pairs of the pattern, the
+ * reordering quality metric of the reference (fewer is better).  height >= 1.
+ * Rows must hold their columns in ascending order for height <= 12 (the CSR contract of
+ * this library and of the reference); taller windows accept any order.  count is a host
+ * pointer; the call synchronises the context's stream.  On error *count is 0 and
+ * sporder_last_error() says why (the reference aborts). */
+SPORDER_API void sporder_count_pillars(sporder_context_t ctx, int32_t n, int32_t nnz,
+                                       const int32_t *d_ptr, const int32_t *d_ind, int32_t height,
+                                       int32_t *count);
+
 /* replaces sporder/include/sporder.h:230-233 */
 typedef enum {
   SPORDER_REORDER_ROWS = 0,

@@ -146,6 +146,20 @@ def spmm_f32(ptr, ind, val, B):
     return Cm
 
 
+def count_pillars(ptr, ind, height, ncols=None):
+    """Distinct (row // height, column) pairs (sporder/src/count_pillars.cu:38-85)."""
+    ptr, ind = _i32(ptr), _i32(ind)
+    n = ptr.size - 1
+    if ncols is None:
+        ncols = max(n, int(ind.max()) + 1 if ind.size else 1)
+    fn = lib().oracle_count_pillars
+    fn.restype = C.c_int64
+    out = fn(C.c_int32(n), C.c_int32(ncols), _p(ptr), _p(ind), C.c_int32(height))
+    if out < 0:
+        raise ValueError("oracle_count_pillars: bad arguments")
+    return int(out)
+
+
 def decode_table(table):
     """packed entries -> (index int32, weight float32) arrays of the same shape."""
     t = np.asarray(table, dtype=np.uint64)

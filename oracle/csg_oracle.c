@@ -499,3 +499,28 @@ ORACLE_API void oracle_set_num_threads(int t) {
   (void)t;
 #endif
 }
+
+/* Pillar count, sporder/src/count_pillars.cu:11-35,38-85: the reference keys every nonzero
+ * with (row / height, column), sorts the keys and counts the distinct ones.  Restated with a
+ * per-window marker array instead of a sort: a column is counted the first time a window
+ * meets it.  Returns -1 on bad arguments. */
+ORACLE_API int64_t oracle_count_pillars(int32_t n, int32_t ncols, const int32_t *ptr,
+                                        const int32_t *ind, int32_t height) {
+  if (n < 1 || ncols < 1 || height < 1) return -1;
+  int32_t *last = (int32_t *)malloc(sizeof(int32_t) * (size_t)ncols);
+  if (!last) return -1;
+  for (int32_t c = 0; c < ncols; ++c) last[c] = -1;
+  int64_t count = 0;
+  for (int32_t r = 0; r < n; ++r) {
+    const int32_t window = r / height;
+    for (int32_t p = ptr[r]; p < ptr[r + 1]; ++p) {
+      const int32_t c = ind[p];
+      if (last[c] != window) {
+        last[c] = window;
+        ++count;
+      }
+    }
+  }
+  free(last);
+  return count;
+}

@@ -91,3 +91,15 @@ def reorder(ptr, ind, new_order, val=None, symmetric=False):
         C.c_void_p(ptr_new.data_ptr()), C.c_void_p(ind_new.data_ptr()),
         C.c_void_p(val_new.data_ptr()) if val is not None else None)
     return (ptr_new, ind_new) if val is None else (ptr_new, ind_new, val_new)
+
+
+def count_pillars(ptr, ind, height):
+    """sporder_count_pillars of the reference (sporder/include/sporder.h:276-279) on int32
+    CUDA torch tensors."""
+    import torch
+    n, nnz = ptr.numel() - 1, ind.numel()
+    out = C.c_int32(0)
+    torch.cuda.synchronize()
+    lib().sporder_count_pillars(_context(), C.c_int32(n), C.c_int32(nnz), C.c_void_p(ptr.data_ptr()),
+                                C.c_void_p(ind.data_ptr()), C.c_int32(int(height)), C.byref(out))
+    return int(out.value)

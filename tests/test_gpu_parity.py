@@ -203,6 +203,35 @@ def test_result_independent_of_repeat_and_context():
     ctx.close()
 
 
+@pytest.mark.parametrize("name", ["band1000", "ragged", "hubsym", "rmat12", "rmat16", "dense_ragged",
+                                  "tiny1"])
+def test_pillar_count_matches_oracle_and_reference(name):
+    from oracle import ref
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build(name)
+    n = ptr.size - 1
+    d_ptr, d_ind = _dev(ptr), _dev(ind)
+    for height in (1, 2, 16, 32, 33, 100, 1024, n + 5):
+        want = oracle.count_pillars(ptr, ind, height)
+        assert sp.count_pillars(d_ptr, d_ind, height) == want
+        if ref.available() and height in (1, 16, 1024):
+            assert ref.count_pillars(d_ptr, d_ind, height) == want
+    assert sp.count_pillars(d_ptr, d_ind, 1) == ind.size  # sporder/tests/smoke.c:98-103
+    with pytest.raises((ValueError, RuntimeError)):
+        sp.count_pillars(d_ptr, d_ind, 0)
+
+
+def test_pillar_count_of_the_reordered_matrix():
+    # the metric is what the reorder is judged by: computed on P A P^T it must equal the
+    # oracle's count on the oracle's reordered matrix
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build("hubsym")
+    order = sp.chunk_similarity_greedy(_dev(ptr), _dev(ind), is_symmetric=True)
+    p2, i2 = sp.reorder(_dev(ptr), _dev(ind), order, symmetric=True)
+    rp, ri = oracle.reorder(ptr, ind, order.cpu().numpy(), symmetric=True)
+    assert sp.count_pillars(p2, i2, 16) == oracle.count_pillars(rp, ri, 16)
+
+
 def test_host_entry_point_matches_device_path():
     sp = _sp()
     ptr, ind, val, sym, params = cases.build("rmat12")

@@ -112,3 +112,17 @@ def test_spmm_oracles_agree():
     c64, cabs = oracle.spmm_f64(ptr, ind, val, B)
     c32 = oracle.spmm_f32(ptr, ind, val, B)
     assert np.all(np.abs(c32 - c64) <= 1e-5 * cabs + 1e-30)
+
+
+@pytest.mark.parametrize("name", ["band1000", "ragged", "hubsym", "rmat12", "stencil48"])
+def test_oracle_pillar_count_against_brute_force(name):
+    # sporder/src/count_pillars.cu:38-85 counts distinct (row // height, column) keys
+    ptr, ind, val, sym, params = cases.build(name)
+    n = ptr.size - 1
+    rows = np.repeat(np.arange(n, dtype=np.int64), np.diff(ptr))
+    for height in (1, 2, 16, 33, 1000, n + 5):
+        brute = np.unique((rows // height) * n + ind).size
+        assert oracle.count_pillars(ptr, ind, height) == brute
+    # the reference's smoke test: one window per row counts every nonzero
+    # (sporder/tests/smoke.c:98-103)
+    assert oracle.count_pillars(ptr, ind, 1) == ind.size
