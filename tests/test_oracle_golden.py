@@ -126,3 +126,17 @@ def test_oracle_pillar_count_against_brute_force(name):
     # the reference's smoke test: one window per row counts every nonzero
     # (sporder/tests/smoke.c:98-103)
     assert oracle.count_pillars(ptr, ind, 1) == ind.size
+
+
+def test_oracle_pillar_count_matches_reference_outputs():
+    # tests/golden/pillars_golden.json: sporder_count_pillars of the reference library on a
+    # B200 (tests/golden/make_pillars_golden.py)
+    import json
+    import os
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "pillars_golden.json")
+    recorded = json.load(open(path))
+    assert sorted(recorded) == sorted(cases.CASES)
+    for name, by_height in recorded.items():
+        ptr, ind, val, sym, params = cases.build(name)
+        for height, want in by_height.items():
+            assert oracle.count_pillars(ptr, ind, int(height)) == want, (name, height)
