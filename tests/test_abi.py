@@ -55,3 +55,10 @@ def test_no_cpu_fallback_message(monkeypatch):
         assert "no CPU fallback" in str(e)
     else:
         raise AssertionError("Context() must fail without a CUDA device")
+
+
+def test_harness_module_imports_without_gpu_or_harness():
+    from chunkedgreedy_b200 import harness
+    assert harness.B200SpMM().name == "sporder-b200-spmm"
+    r = harness.ReorderResult(row_perm=None, reorder_time_ms=1.0)
+    assert r.prep_time_ms == 0.0 and r.timing_breakdown == {}

@@ -232,6 +232,32 @@ def test_pillar_count_of_the_reordered_matrix():
     assert sp.count_pillars(p2, i2, 16) == oracle.count_pillars(rp, ri, 16)
 
 
+def test_harness_method_modules():
+    # the shapes the reference's own scripts call: reorder_bench/methods/sporder_csg.py:25-70
+    # and spmm_bench/base.py:8-65
+    import scipy.sparse
+    from chunkedgreedy_b200 import harness
+    ptr, ind, val, sym, params = cases.build("hubsym")
+    n = ptr.size - 1
+    csr = scipy.sparse.csr_matrix((val, ind, ptr), shape=(n, n))
+    res = harness.reorder(csr, {"k": 0, "oversampling": 0.0, "chunk_size": 0})
+    assert res.effective_params["is_symmetric"] is False  # random values: A != A^T
+    assert res.row_perm.dtype == np.int64
+    assert np.array_equal(res.row_perm, oracle.csg(ptr, ind, False))
+    assert res.reorder_time_ms > 0 and set(res.timing_breakdown) == {"csr2csc_ms", "similarity_ms",
+                                                                     "chunk_greedy_ms"}
+    pattern = scipy.sparse.csr_matrix((np.ones_like(val), ind, ptr), shape=(n, n))
+    assert harness.reorder(pattern, {}).effective_params["is_symmetric"] is True
+    m = harness.B200SpMM()
+    m.build()
+    prepared = m.prepare(csr)
+    B = np.random.default_rng(3).standard_normal((n, 32)).astype(np.float32)
+    C, kernel_ms = m.run(prepared, torch.from_numpy(B).cuda())
+    c64, cabs = oracle.spmm_f64(ptr, ind, val, B)
+    assert kernel_ms > 0
+    assert np.all(np.abs(C.cpu().numpy() - c64) <= 1e-5 * cabs + 1e-30)
+
+
 def test_host_entry_point_matches_device_path():
     sp = _sp()
     ptr, ind, val, sym, params = cases.build("rmat12")
