@@ -19,7 +19,8 @@ import ctypes as C
 from . import _lib
 
 __all__ = ["Context", "chunk_similarity_greedy", "reorder", "spmm", "csg_table",
-           "chunk_similarity_greedy_host", "kernel_launches", "count_pillars"]
+           "chunk_similarity_greedy_host", "kernel_launches", "count_pillars",
+           "similarity_graph"]
 
 _default_ctx = {}
 
@@ -198,6 +199,43 @@ def chunk_similarity_greedy_host(ptr, ind, *, is_symmetric=False, k=0, oversampl
     if rc != 0:
         _lib.check()
     return out
+
+
+def similarity_graph(ptr, ind, *, is_symmetric=False, k=0, oversampling=0.0, with_timing=False,
+                     with_stats=False, ctx=None):
+    """Weighted top-k Dice-similarity graph (sporder/python/sporder/__init__.py:200-259):
+    ``(indices, weights)``, two ``(n, k_used)`` CUDA tensors (int32 / float32), entries by
+    descending weight per row, unused entries index -1 and weight 0; a ``timing`` dict
+    (wall_ms, csr2csc_ms, similarity_ms, unpack_ms) and/or a ``stats`` dict (k_used, m_used,
+    avg_degree, avg_edge_weight, zero_degree_rows) are appended when requested."""
+    torch = _torch()
+    ptr = _as_tensor(ptr, torch.int32, "ptr")
+    ind = _as_tensor(ind, torch.int32, "ind")
+    n, nnz = _sizes(ptr, ind)
+    kk = int(k) if k > 0 else min(32, max(16, 2 * (nnz // max(n, 1))))  # sporder.cpp:75-77
+    ctx = _ctx(ctx)
+    lib = _lib.load()
+    with torch.cuda.device(ptr.device):
+        _enter(ctx, ptr)
+        idx = torch.empty((n, kk), dtype=torch.int32, device=ptr.device)
+        wgt = torch.empty((n, kk), dtype=torch.float32, device=ptr.device)
+        timing, stats = _lib.SimTiming(), _lib.SimStats()
+        rc = lib.sporder_similarity_graph(
+            ctx.handle, n, nnz, ptr.data_ptr(), ind.data_ptr(), bool(is_symmetric), kk,
+            float(oversampling), idx.data_ptr(), wgt.data_ptr(),
+            C.byref(timing) if with_timing else None, C.byref(stats) if with_stats else None)
+    if rc < 0:
+        msg = _lib.last_error() or "sporder_similarity_graph failed"
+        raise ValueError(msg) if "expect" in msg or "must be" in msg else RuntimeError(msg)
+    result = (idx, wgt)
+    if with_timing:
+        result += (dict(wall_ms=timing.wall_ms, csr2csc_ms=timing.csr2csc_ms,
+                        similarity_ms=timing.similarity_ms, unpack_ms=timing.unpack_ms),)
+    if with_stats:
+        result += (dict(k_used=stats.k_used, m_used=stats.m_used, avg_degree=stats.avg_degree,
+                        avg_edge_weight=stats.avg_edge_weight,
+                        zero_degree_rows=stats.zero_degree_rows),)
+    return result
 
 
 def count_pillars(ptr, ind, height, *, ctx=None):

@@ -28,6 +28,16 @@ class CsgStats(C.Structure):
 
 # every symbol include/sporder_b200.h declares: name -> (restype, argtypes)
 _P = C.c_void_p
+class SimTiming(C.Structure):
+    _fields_ = [("wall_ms", C.c_double), ("csr2csc_ms", C.c_float), ("similarity_ms", C.c_float),
+                ("unpack_ms", C.c_float)]
+
+
+class SimStats(C.Structure):
+    _fields_ = [("k_used", C.c_int32), ("m_used", C.c_int32), ("avg_degree", C.c_double),
+                ("avg_edge_weight", C.c_double), ("zero_degree_rows", C.c_int32)]
+
+
 SYMBOLS = {
     "sporder_context_create": (_P, []),
     "sporder_context_destroy": (None, [_P]),
@@ -52,6 +62,9 @@ SYMBOLS = {
     "sporder_spmm_async": (C.c_int32, [_P, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P]),
     "sporder_spmm_static": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P]),
     "sporder_kernel_launches": (C.c_uint64, []),
+    "sporder_similarity_graph": (C.c_int32, [_P, C.c_int32, C.c_int32, _P, _P, C.c_bool, C.c_int32,
+                                             C.c_float, _P, _P, C.POINTER(SimTiming),
+                                             C.POINTER(SimStats)]),
     "sporder_count_pillars": (None, [_P, C.c_int32, C.c_int32, _P, _P, C.c_int32,
                                      C.POINTER(C.c_int32)]),
 }

@@ -221,6 +221,89 @@ bool run_csg(Context &ctx, int32_t n, int32_t ncols, int32_t row_base, int32_t n
 }
 
 
+// packed table -> separate arrays; an empty entry (0) reads as index -1, weight 0
+// (sporder/src/similarity_graph.cu:13-23)
+__global__ void __launch_bounds__(256) unpack_table_kernel(size_t count, const uint64_t *__restrict__ table,
+                                                           int32_t *__restrict__ indices,
+                                                           float *__restrict__ weights) {
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const uint64_t e = table[i];
+    indices[i] = static_cast<int32_t>(static_cast<uint32_t>(e)) - 1;
+    weights[i] = __uint_as_float(static_cast<uint32_t>(e >> 32));
+  }
+}
+
+// The public top-k similarity graph (sporder/src/similarity_graph.cu:26-107,
+// sporder/src/sporder.cpp:69-91): the same candidate stream, sketch and top-k selection as
+// csg with the whole matrix as the one chunk (sporder/src/common/similarity_top_k.cu:10-51),
+// other defaults (k = min(32, max(16, 2 nnz / n)), oversampling 2), results unpacked.
+bool run_similarity_graph(Context &ctx, int32_t n, int32_t nnz, const int32_t *d_ptr, const int32_t *d_ind,
+                          int32_t k, float ovs, int32_t *d_indices, float *d_weights,
+                          sporder_sim_timing_t *timing, sporder_sim_stats_t *stats, int32_t *k_used) {
+  const auto wall0 = std::chrono::steady_clock::now();
+  CSG_REQUIRE(n >= 1, "n must be >= 1 (got %d)", n);
+  CSG_REQUIRE(nnz >= 0, "nnz must be >= 0 (got %d)", nnz);
+  if (k <= 0) {
+    int32_t a = 2 * (nnz / n);
+    if (a < 16) a = 16;
+    if (a > 32) a = 32;
+    k = a;
+  }
+  if (ovs <= 0.0f) ovs = 2.0f;
+  CsgParams p;
+  if (!resolve_params(n, nnz, k, ovs, n, &p)) return false;
+  if (k_used) *k_used = p.k;
+  if (stats) {
+    std::memset(stats, 0, sizeof(*stats));
+    stats->k_used = p.k;
+    stats->m_used = p.m_used;
+  }
+  CSG_REQUIRE(d_ptr && (d_ind || nnz == 0), "null CSR arrays");
+  CSG_REQUIRE(d_indices && d_weights, "null output arrays");
+  CSG_CUDA(cudaSetDevice(ctx.device));
+  CsgScratch s;
+  if (!plan_scratch(ctx, n, nnz, p, nullptr, &s)) return false;
+  cudaStream_t st = ctx.stream;
+  if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[0], st));
+  if (!launch_transpose(ctx, n, n, nnz, p.chunk, d_ptr, d_ind, s)) return false;
+  if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
+  if (!launch_sketch(ctx, n, nnz, p, d_ptr, s, 0)) return false;
+  if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[2], st));
+  if (stats && !launch_table_stats(ctx, n, p.k, s.table, s.ctrl)) return false;
+  if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[3], st));
+  const size_t count = static_cast<size_t>(n) * p.k;
+  size_t grid = (count + 255) / 256;
+  if (grid > static_cast<size_t>(ctx.num_sms) * 16) grid = static_cast<size_t>(ctx.num_sms) * 16;
+  unpack_table_kernel<<<static_cast<unsigned>(grid), 256, 0, st>>>(count, s.table, d_indices, d_weights);
+  CSG_CUDA(cudaGetLastError());
+  count_launches(1);
+  if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[4], st));
+  ChainStatsHost hs;
+  if (stats)
+    CSG_CUDA(cudaMemcpyAsync(&hs, s.ctrl + CTRL_STATS, sizeof(hs), cudaMemcpyDeviceToHost, st));
+  CSG_CUDA(cudaMemcpyAsync(ctx.h_pinned, s.ctrl + CTRL_BAD_INPUT, sizeof(uint32_t),
+                           cudaMemcpyDeviceToHost, st));
+  CSG_CUDA(cudaStreamSynchronize(st));
+  CSG_CUDA(cudaGetLastError());
+  CSG_REQUIRE(ctx.h_pinned[0] == 0,
+              "malformed CSR: row pointers must be non-decreasing inside [0, nnz] (results unspecified)");
+  if (stats) {  // sporder/src/similarity_graph.cu:99-104
+    stats->avg_degree = static_cast<double>(hs.total_degree) / n;
+    stats->avg_edge_weight =
+        hs.total_degree > 0 ? hs.total_weight / static_cast<double>(hs.total_degree) : 0.0;
+    stats->zero_degree_rows = hs.zero_degree_rows;
+  }
+  if (timing) {
+    CSG_CUDA(cudaEventElapsedTime(&timing->csr2csc_ms, ctx.ev[0], ctx.ev[1]));
+    CSG_CUDA(cudaEventElapsedTime(&timing->similarity_ms, ctx.ev[1], ctx.ev[2]));
+    CSG_CUDA(cudaEventElapsedTime(&timing->unpack_ms, ctx.ev[3], ctx.ev[4]));
+    timing->wall_ms =
+        std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - wall0).count();
+  }
+  return true;
+}
+
 // Pillar count (sporder/src/count_pillars.cu:38-85): windows of up to 12 rows by searching
 // the window's earlier rows, taller windows as the column groups of the chunk-local
 // transpose with the window as the chunk.  Measured on the 65 M-nonzero R-MAT matrix the
@@ -425,6 +508,23 @@ int32_t sporder_chunk_similarity_greedy_host(sporder_context_t ctx, int32_t n, i
     return ok;
   };
   return run() ? 0 : -1;
+}
+
+int32_t sporder_similarity_graph(sporder_context_t ctx, int32_t n, int32_t nnz, const int32_t *d_ptr,
+                                 const int32_t *d_ind, bool is_symmetric, int32_t k, float oversampling,
+                                 int32_t *d_indices, float *d_weights, sporder_sim_timing_t *timing,
+                                 sporder_sim_stats_t *stats) {
+  (void)is_symmetric;
+  csg::clear_error();
+  if (!ctx) {
+    csg::set_error("null context");
+    return -1;
+  }
+  int32_t k_used = -1;
+  if (!csg::run_similarity_graph(ctx->c, n, nnz, d_ptr, d_ind, k, oversampling, d_indices, d_weights,
+                                 timing, stats, &k_used))
+    return -1;
+  return k_used;
 }
 
 void sporder_count_pillars(sporder_context_t ctx, int32_t n, int32_t nnz, const int32_t *d_ptr,

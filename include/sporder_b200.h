@@ -71,6 +71,37 @@ SPORDER_API void sporder_chunk_similarity_greedy(
     bool is_symmetric, int32_t k, float oversampling, int32_t chunk_size, int32_t *d_new_order,
     sporder_csg_timing_t *timing, sporder_csg_stats_t *stats);
 
+/* replaces sporder/include/sporder.h:312-317 (same layout) */
+typedef struct {
+  double wall_ms;
+  float csr2csc_ms;    /* here: the transpose with the matrix as one chunk */
+  float similarity_ms; /* sketch + top-k */
+  float unpack_ms;
+} sporder_sim_timing_t;
+
+/* replaces sporder/include/sporder.h:322-328 (same layout) */
+typedef struct {
+  int32_t k_used;
+  int32_t m_used;
+  double avg_degree;
+  double avg_edge_weight;
+  int32_t zero_degree_rows;
+} sporder_sim_stats_t;
+
+/* replaces sporder/include/sporder.h:330-335 (sporder/src/similarity_graph.cu:26-107):
+ * for each row up to k rows with the largest sketched Dice similarity, as
+ * d_indices[r * k + j] / d_weights[r * k + j], unused entries index -1, weight 0.
+ * k <= 0 -> min(32, max(16, 2 * (nnz / n))); oversampling <= 0 -> 2.0
+ * (sporder/src/sporder.cpp:75-80).  The outputs must hold n * k entries for the k in
+ * use; the return value is that k (the reference returns nothing), -1 on error.
+ * is_symmetric does not change the result (see sporder_chunk_similarity_greedy). */
+SPORDER_API int32_t sporder_similarity_graph(sporder_context_t ctx, int32_t n, int32_t nnz,
+                                             const int32_t *d_ptr, const int32_t *d_ind,
+                                             bool is_symmetric, int32_t k, float oversampling,
+                                             int32_t *d_indices, float *d_weights,
+                                             sporder_sim_timing_t *timing,
+                                             sporder_sim_stats_t *stats);
+
 /* replaces sporder/include/sporder.h:276-279 (sporder/src/count_pillars.cu:38-85):
  * *count = number of distinct (row / height, column) pairs of the pattern, the
  * reordering quality metric of the reference (fewer is better).  height >= 1.

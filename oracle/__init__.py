@@ -146,6 +146,20 @@ def spmm_f32(ptr, ind, val, B):
     return Cm
 
 
+def similarity_graph(ptr, ind, k=0, oversampling=0.0):
+    """The global top-k graph (sporder/src/similarity_graph.cu:26-107): the csg sketch with
+    the whole matrix as the one chunk (sporder/src/common/similarity_top_k.cu:10-51) and the
+    defaults of sporder/src/sporder.cpp:75-80.  Returns (indices, weights), shape (n, k)."""
+    ptr, ind = _i32(ptr), _i32(ind)
+    n, nnz = ptr.size - 1, ind.size
+    if k <= 0:
+        k = min(32, max(16, 2 * (nnz // n)))
+    if oversampling <= 0.0:
+        oversampling = 2.0
+    _, table = csg(ptr, ind, False, k=k, oversampling=oversampling, chunk_size=n, with_table=True)
+    return decode_table(table.reshape(n, k))
+
+
 def count_pillars(ptr, ind, height, ncols=None):
     """Distinct (row // height, column) pairs (sporder/src/count_pillars.cu:38-85)."""
     ptr, ind = _i32(ptr), _i32(ind)

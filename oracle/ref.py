@@ -103,3 +103,20 @@ def count_pillars(ptr, ind, height):
     lib().sporder_count_pillars(_context(), C.c_int32(n), C.c_int32(nnz), C.c_void_p(ptr.data_ptr()),
                                 C.c_void_p(ind.data_ptr()), C.c_int32(int(height)), C.byref(out))
     return int(out.value)
+
+
+def similarity_graph(ptr, ind, is_symmetric=False, k=0, oversampling=0.0):
+    """sporder_similarity_graph of the reference (sporder/include/sporder.h:330-335) on int32
+    CUDA torch tensors; returns (indices, weights) tensors of shape (n, k)."""
+    import torch
+    n, nnz = ptr.numel() - 1, ind.numel()
+    kk = int(k) if k > 0 else min(32, max(16, 2 * (nnz // n)))
+    idx = torch.empty((n, kk), dtype=torch.int32, device=ptr.device)
+    wgt = torch.empty((n, kk), dtype=torch.float32, device=ptr.device)
+    torch.cuda.synchronize()
+    lib().sporder_similarity_graph(
+        _context(), C.c_int32(n), C.c_int32(nnz), C.c_void_p(ptr.data_ptr()),
+        C.c_void_p(ind.data_ptr()), C.c_bool(bool(is_symmetric)), C.c_int32(kk),
+        C.c_float(oversampling), C.c_void_p(idx.data_ptr()), C.c_void_p(wgt.data_ptr()), None, None)
+    torch.cuda.synchronize()
+    return idx, wgt

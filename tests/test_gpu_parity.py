@@ -232,6 +232,26 @@ def test_pillar_count_of_the_reordered_matrix():
     assert sp.count_pillars(p2, i2, 16) == oracle.count_pillars(rp, ri, 16)
 
 
+@pytest.mark.parametrize("name", ["band1000", "ragged", "hubsym", "rmat12", "stencil48", "dense_ragged"])
+def test_similarity_graph_matches_oracle_and_reference(name):
+    from oracle import ref
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build(name)
+    d_ptr, d_ind = _dev(ptr), _dev(ind)
+    for kw in (dict(), dict(k=8, oversampling=4.0), dict(k=40, oversampling=3.0)):
+        idx, wgt, stats = sp.similarity_graph(d_ptr, d_ind, is_symmetric=sym, with_stats=True, **kw)
+        o_idx, o_wgt = oracle.similarity_graph(ptr, ind, **kw)
+        assert np.array_equal(idx.cpu().numpy(), o_idx)
+        assert np.array_equal(wgt.cpu().numpy().view(np.uint32), o_wgt.view(np.uint32))
+        assert stats["k_used"] == o_idx.shape[1]
+        assert stats["zero_degree_rows"] == int((o_idx[:, 0] < 0).sum())
+        assert abs(stats["avg_degree"] - (o_idx >= 0).sum() / o_idx.shape[0]) < 1e-9
+        if ref.available():
+            r_idx, r_wgt = ref.similarity_graph(d_ptr, d_ind, sym, **kw)
+            assert np.array_equal(r_idx.cpu().numpy(), o_idx)
+            assert np.array_equal(r_wgt.cpu().numpy().view(np.uint32), o_wgt.view(np.uint32))
+
+
 def test_harness_method_modules():
     # the shapes the reference's own scripts call: reorder_bench/methods/sporder_csg.py:25-70
     # and spmm_bench/base.py:8-65
