@@ -20,7 +20,7 @@ from . import _lib
 
 __all__ = ["Context", "chunk_similarity_greedy", "reorder", "spmm", "csg_table",
            "chunk_similarity_greedy_host", "kernel_launches", "count_pillars",
-           "similarity_graph"]
+           "similarity_graph", "chunk_greedy"]
 
 _default_ctx = {}
 
@@ -199,6 +199,36 @@ def chunk_similarity_greedy_host(ptr, ind, *, is_symmetric=False, k=0, oversampl
     if rc != 0:
         _lib.check()
     return out
+
+
+def chunk_greedy(ptr, ind, *, is_symmetric=False, k=0, oversampling=0.0, chunk_size=0,
+                 with_timing=False, with_stats=False, ctx=None):
+    """Chunked greedy seriation on the GLOBAL top-k graph (the reference's ``cg``;
+    sporder/include/sporder.h:169-182): ``new_order`` [, timing dict] [, stats dict with
+    the csg fields plus ``cut_weight_fraction``]."""
+    torch = _torch()
+    ptr = _as_tensor(ptr, torch.int32, "ptr")
+    ind = _as_tensor(ind, torch.int32, "ind")
+    n, nnz = _sizes(ptr, ind)
+    ctx = _ctx(ctx)
+    lib = _lib.load()
+    with torch.cuda.device(ptr.device):
+        _enter(ctx, ptr)
+        order = torch.empty(n, dtype=torch.int32, device=ptr.device)
+        timing, stats = _lib.CsgTiming(), _lib.CgStats()
+        lib.sporder_chunk_greedy(
+            ctx.handle, n, nnz, ptr.data_ptr(), ind.data_ptr(), bool(is_symmetric), int(k),
+            float(oversampling), int(chunk_size), order.data_ptr(),
+            C.byref(timing) if with_timing else None, C.byref(stats) if with_stats else None)
+    msg = _lib.last_error()
+    if msg:
+        raise ValueError(msg) if "expect" in msg or "must be" in msg else RuntimeError(msg)
+    result = (order,)
+    if with_timing:
+        result += (_timing_dict(timing),)
+    if with_stats:
+        result += ({f: getattr(stats, f) for f, _ in _lib.CgStats._fields_},)
+    return result if len(result) > 1 else result[0]
 
 
 def similarity_graph(ptr, ind, *, is_symmetric=False, k=0, oversampling=0.0, with_timing=False,

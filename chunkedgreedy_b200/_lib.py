@@ -28,6 +28,13 @@ class CsgStats(C.Structure):
 
 # every symbol include/sporder_b200.h declares: name -> (restype, argtypes)
 _P = C.c_void_p
+class CgStats(C.Structure):
+    _fields_ = [("k_used", C.c_int32), ("m_used", C.c_int32), ("avg_degree", C.c_double),
+                ("avg_edge_weight", C.c_double), ("zero_degree_rows", C.c_int32),
+                ("chunk_size_used", C.c_int32), ("chain_restarts", C.c_int32),
+                ("avg_followed_weight", C.c_double), ("cut_weight_fraction", C.c_double)]
+
+
 class SimTiming(C.Structure):
     _fields_ = [("wall_ms", C.c_double), ("csr2csc_ms", C.c_float), ("similarity_ms", C.c_float),
                 ("unpack_ms", C.c_float)]
@@ -62,6 +69,8 @@ SYMBOLS = {
     "sporder_spmm_async": (C.c_int32, [_P, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P]),
     "sporder_spmm_static": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P]),
     "sporder_kernel_launches": (C.c_uint64, []),
+    "sporder_chunk_greedy": (None, [_P, C.c_int32, C.c_int32, _P, _P, C.c_bool, C.c_int32, C.c_float,
+                                    C.c_int32, _P, C.POINTER(CsgTiming), C.POINTER(CgStats)]),
     "sporder_similarity_graph": (C.c_int32, [_P, C.c_int32, C.c_int32, _P, _P, C.c_bool, C.c_int32,
                                              C.c_float, _P, _P, C.POINTER(SimTiming),
                                              C.POINTER(SimStats)]),

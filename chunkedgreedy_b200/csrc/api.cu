@@ -86,6 +86,7 @@ struct ChainStatsHost {
   int32_t restarts;
   int32_t links;
   int32_t pad;
+  double in_chunk_weight;
 };
 
 size_t greedy_bitmap_words(int32_t n, int32_t chunk) {
@@ -98,7 +99,7 @@ size_t greedy_bitmap_words(int32_t n, int32_t chunk) {
 
 // Lays out the scratch of one csg call in the context workspace.
 bool plan_scratch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, uint64_t *user_table,
-                  CsgScratch *s) {
+                  CsgScratch *s, int32_t greedy_chunk = 0) {
   Arena ar;
   const size_t z = static_cast<size_t>(nnz > 0 ? nnz : 1);
   const size_t o_keyA = ar.take(4 * z), o_keyB = ar.take(4 * z);
@@ -107,7 +108,9 @@ bool plan_scratch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, uint
   const size_t o_work = ar.take(4 * static_cast<size_t>(n));
   const size_t o_list = ar.take(4 * static_cast<size_t>(n));
   const size_t o_ctrl = ar.take(4 * CTRL_WORDS);
-  const size_t bw = greedy_bitmap_words(n, p.chunk);
+  // (the greedy stage may run with another chunk size than the sketch: chunk_greedy)
+  size_t bw = greedy_bitmap_words(n, p.chunk);
+  if (greedy_chunk > 0 && greedy_bitmap_words(n, greedy_chunk) > bw) bw = greedy_bitmap_words(n, greedy_chunk);
   const size_t o_bm = ar.take(4 * (bw ? bw : 1));
   // heavy chunks hold more than 15360 nonzeros each and are cut into tiles of 4096
   const size_t chunks = (static_cast<size_t>(n) + p.chunk - 1) / p.chunk;
@@ -298,6 +301,71 @@ bool run_similarity_graph(Context &ctx, int32_t n, int32_t nnz, const int32_t *d
     CSG_CUDA(cudaEventElapsedTime(&timing->csr2csc_ms, ctx.ev[0], ctx.ev[1]));
     CSG_CUDA(cudaEventElapsedTime(&timing->similarity_ms, ctx.ev[1], ctx.ev[2]));
     CSG_CUDA(cudaEventElapsedTime(&timing->unpack_ms, ctx.ev[3], ctx.ev[4]));
+    timing->wall_ms =
+        std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - wall0).count();
+  }
+  return true;
+}
+
+// Chunked greedy on the global graph (sporder/src/cg/chunk_greedy.cu:118-163,
+// sporder/src/sporder.cpp:112-138): the top-k graph of run_similarity_graph with the csg
+// defaults (k = min(256, max(16, nnz / n)), oversampling 4), then the greedy chains inside
+// chunks of chunk_size rows, candidates outside the chunk skipped.
+bool run_chunk_greedy(Context &ctx, int32_t n, int32_t nnz, const int32_t *d_ptr, const int32_t *d_ind,
+                      int32_t k, float ovs, int32_t chunk, int32_t *d_new_order,
+                      sporder_cg_timing_t *timing, sporder_cg_stats_t *stats) {
+  const auto wall0 = std::chrono::steady_clock::now();
+  CsgParams pg;  // greedy: the caller's chunk; also resolves k and oversampling
+  if (!resolve_params(n, nnz, k, ovs, chunk, &pg)) return false;
+  CsgParams ps = pg;  // sketch: the whole matrix is the chunk
+  ps.chunk = n;
+  if (stats) {
+    std::memset(stats, 0, sizeof(*stats));
+    stats->k_used = pg.k;
+    stats->m_used = pg.m_used;
+    stats->chunk_size_used = pg.chunk;
+  }
+  CSG_REQUIRE(d_ptr && (d_ind || nnz == 0), "null CSR arrays");
+  CSG_REQUIRE(d_new_order, "null d_new_order");
+  CSG_CUDA(cudaSetDevice(ctx.device));
+  CsgScratch s;
+  if (!plan_scratch(ctx, n, nnz, ps, nullptr, &s, pg.chunk)) return false;
+  cudaStream_t st = ctx.stream;
+  if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[0], st));
+  if (!launch_transpose(ctx, n, n, nnz, ps.chunk, d_ptr, d_ind, s)) return false;
+  if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
+  if (!launch_sketch(ctx, n, nnz, ps, d_ptr, s, 0)) return false;
+  if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[2], st));
+  if (stats) {
+    if (!launch_table_stats(ctx, n, pg.k, s.table, s.ctrl)) return false;
+    if (!launch_in_chunk_weight(ctx, n, pg.k, pg.chunk, s.table, s.ctrl)) return false;
+  }
+  if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[3], st));
+  if (!launch_greedy(ctx, n, pg, s, d_new_order, stats != nullptr, 0)) return false;
+  if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[4], st));
+  ChainStatsHost hs;
+  if (stats)
+    CSG_CUDA(cudaMemcpyAsync(&hs, s.ctrl + CTRL_STATS, sizeof(hs), cudaMemcpyDeviceToHost, st));
+  CSG_CUDA(cudaMemcpyAsync(ctx.h_pinned, s.ctrl + CTRL_BAD_INPUT, sizeof(uint32_t),
+                           cudaMemcpyDeviceToHost, st));
+  CSG_CUDA(cudaStreamSynchronize(st));
+  CSG_CUDA(cudaGetLastError());
+  CSG_REQUIRE(ctx.h_pinned[0] == 0,
+              "malformed CSR: row pointers must be non-decreasing inside [0, nnz] (results unspecified)");
+  if (stats) {  // sporder/src/cg/stats_collector.cu:52-73
+    stats->avg_degree = static_cast<double>(hs.total_degree) / n;
+    stats->avg_edge_weight =
+        hs.total_degree > 0 ? hs.total_weight / static_cast<double>(hs.total_degree) : 0.0;
+    stats->zero_degree_rows = hs.zero_degree_rows;
+    stats->chain_restarts = hs.restarts;
+    stats->avg_followed_weight = hs.links > 0 ? hs.link_weight_sum / hs.links : 0.0;
+    double cut = hs.total_weight > 0.0 ? 1.0 - hs.in_chunk_weight / hs.total_weight : 0.0;
+    stats->cut_weight_fraction = cut < 0.0 ? 0.0 : (cut > 1.0 ? 1.0 : cut);
+  }
+  if (timing) {
+    CSG_CUDA(cudaEventElapsedTime(&timing->csr2csc_ms, ctx.ev[0], ctx.ev[1]));
+    CSG_CUDA(cudaEventElapsedTime(&timing->similarity_ms, ctx.ev[1], ctx.ev[2]));
+    CSG_CUDA(cudaEventElapsedTime(&timing->chunk_greedy_ms, ctx.ev[3], ctx.ev[4]));
     timing->wall_ms =
         std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - wall0).count();
   }
@@ -508,6 +576,20 @@ int32_t sporder_chunk_similarity_greedy_host(sporder_context_t ctx, int32_t n, i
     return ok;
   };
   return run() ? 0 : -1;
+}
+
+void sporder_chunk_greedy(sporder_context_t ctx, int32_t n, int32_t nnz, const int32_t *d_ptr,
+                          const int32_t *d_ind, bool is_symmetric, int32_t k, float oversampling,
+                          int32_t chunk_size, int32_t *d_new_order, sporder_cg_timing_t *timing,
+                          sporder_cg_stats_t *stats) {
+  (void)is_symmetric;
+  csg::clear_error();
+  if (!ctx) {
+    csg::set_error("null context");
+    return;
+  }
+  csg::run_chunk_greedy(ctx->c, n, nnz, d_ptr, d_ind, k, oversampling, chunk_size, d_new_order, timing,
+                        stats);
 }
 
 int32_t sporder_similarity_graph(sporder_context_t ctx, int32_t n, int32_t nnz, const int32_t *d_ptr,

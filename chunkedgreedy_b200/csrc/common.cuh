@@ -129,6 +129,8 @@ bool launch_greedy(Context &ctx, int32_t n, const CsgParams &p, CsgScratch &s,
 bool launch_pillars_search(Context &ctx, int32_t n, int32_t nnz, int32_t height, const int32_t *d_ptr,
                            const int32_t *d_ind, unsigned long long *d_count, uint32_t *d_bad);
 bool launch_pillars_groups(Context &ctx, int32_t nnz, const int32_t *seg_rank, unsigned long long *d_count);
+bool launch_in_chunk_weight(Context &ctx, int32_t n, int32_t k, int32_t chunk, const uint64_t *table,
+                            uint32_t *ctrl);
 bool launch_table_stats(Context &ctx, int32_t n, int32_t k, const uint64_t *table, uint32_t *ctrl);
 
 bool launch_reorder(Context &ctx, int32_t n, int32_t nnz, const int32_t *d_ptr_old,

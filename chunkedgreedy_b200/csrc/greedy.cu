@@ -37,6 +37,7 @@ struct ChainStats {  // lives at ctrl[CTRL_STATS ...]
   int32_t restarts;
   int32_t links;
   int32_t pad;
+  double in_chunk_weight;  // table weights whose candidate lies in the row's own chunk
 };
 
 __global__ void __launch_bounds__(G_WARPS * 32) greedy_kernel(GreedyArgs a) {
@@ -172,7 +173,41 @@ __global__ void table_stats_kernel(int32_t n, int32_t k, const uint64_t *__restr
   }
 }
 
+// Weight of the table entries that stay inside their row's chunk, for the fraction of the
+// graph a chunked ordering cuts (sporder/src/cg/chunk_greedy.cu:66-68,111-112;
+// cg/stats_collector.cu:66-72).  Summed in fp64.
+__global__ void __launch_bounds__(256) in_chunk_weight_kernel(int32_t n, int32_t k, int32_t chunk,
+                                                              const uint64_t *__restrict__ table,
+                                                              uint32_t *ctrl) {
+  double mine = 0.0;
+  for (int32_t r = blockIdx.x * blockDim.x + threadIdx.x; r < n; r += gridDim.x * blockDim.x) {
+    const int64_t start = static_cast<int64_t>(r / chunk) * chunk;
+    const int64_t end = start + chunk < n ? start + chunk : n;
+    const uint64_t *row = table + static_cast<size_t>(r) * k;
+    for (int32_t j = 0; j < k; ++j) {
+      const uint64_t e = row[j];
+      if (e == 0) break;
+      const int32_t cand = entry_index(e);
+      if (cand >= start && cand < end) mine += static_cast<double>(__uint_as_float(entry_weight_bits(e)));
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) mine += __shfl_down_sync(FULL, mine, off);
+  if ((threadIdx.x & 31) == 0 && mine != 0.0)
+    atomicAdd(&reinterpret_cast<ChainStats *>(ctrl + CTRL_STATS)->in_chunk_weight, mine);
+}
+
 }  // namespace
+
+bool launch_in_chunk_weight(Context &ctx, int32_t n, int32_t k, int32_t chunk, const uint64_t *table,
+                            uint32_t *ctrl) {
+  int grid = (n + 255) / 256;
+  if (grid > ctx.num_sms * 8) grid = ctx.num_sms * 8;
+  in_chunk_weight_kernel<<<grid, 256, 0, ctx.stream>>>(n, k, chunk, table, ctrl);
+  CSG_CUDA(cudaGetLastError());
+  count_launches(1);
+  return true;
+}
 
 bool launch_greedy(Context &ctx, int32_t n, const CsgParams &p, CsgScratch &s,
                    int32_t *d_new_order, bool with_stats, int32_t row_base) {

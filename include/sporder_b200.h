@@ -71,6 +71,38 @@ SPORDER_API void sporder_chunk_similarity_greedy(
     bool is_symmetric, int32_t k, float oversampling, int32_t chunk_size, int32_t *d_new_order,
     sporder_csg_timing_t *timing, sporder_csg_stats_t *stats);
 
+/* replaces sporder/include/sporder.h:128-133 (same layout) */
+typedef struct {
+  double wall_ms;
+  float csr2csc_ms;
+  float similarity_ms;
+  float chunk_greedy_ms;
+} sporder_cg_timing_t;
+
+/* replaces sporder/include/sporder.h:154-167 (same layout) */
+typedef struct {
+  int32_t k_used;
+  int32_t m_used;
+  double avg_degree;
+  double avg_edge_weight;
+  int32_t zero_degree_rows;
+  int32_t chunk_size_used;
+  int32_t chain_restarts;
+  double avg_followed_weight;
+  double cut_weight_fraction; /* edge weight crossing chunk boundaries over total edge weight */
+} sporder_cg_stats_t;
+
+/* replaces sporder/include/sporder.h:176-182 (sporder/src/cg/chunk_greedy.cu:118-163): the
+ * top-k graph of the WHOLE matrix (as sporder_similarity_graph, with the defaults
+ * k <= 0 -> min(256, max(16, nnz / n)), oversampling <= 0 -> 4.0, chunk_size <= 0 -> 1024 of
+ * sporder/src/sporder.cpp:118-126), then greedy chains inside chunks of chunk_size rows;
+ * neighbours outside a row's chunk are skipped.  new2old permutation, as csg. */
+SPORDER_API void sporder_chunk_greedy(sporder_context_t ctx, int32_t n, int32_t nnz,
+                                      const int32_t *d_ptr, const int32_t *d_ind, bool is_symmetric,
+                                      int32_t k, float oversampling, int32_t chunk_size,
+                                      int32_t *d_new_order, sporder_cg_timing_t *timing,
+                                      sporder_cg_stats_t *stats);
+
 /* replaces sporder/include/sporder.h:312-317 (same layout) */
 typedef struct {
   double wall_ms;

@@ -160,6 +160,30 @@ def similarity_graph(ptr, ind, k=0, oversampling=0.0):
     return decode_table(table.reshape(n, k))
 
 
+def chunk_greedy(ptr, ind, k=0, oversampling=0.0, chunk_size=0):
+    """The reference's cg (sporder/src/cg/chunk_greedy.cu:118-163): global top-k graph with
+    the defaults of sporder/src/sporder.cpp:118-126, then greedy chains per chunk.  Returns
+    (order, stats dict) with the fraction of table weight that crosses chunk boundaries."""
+    ptr, ind = _i32(ptr), _i32(ind)
+    n, nnz = ptr.size - 1, ind.size
+    if k <= 0:
+        k = min(256, max(16, nnz // n))
+    if oversampling <= 0.0:
+        oversampling = 4.0
+    if chunk_size <= 0:
+        chunk_size = 1024
+    _, table = csg(ptr, ind, False, k=k, oversampling=oversampling, chunk_size=n, with_table=True)
+    table = table.reshape(n, k)
+    order, st = greedy(table, n, chunk_size)
+    idx, w = decode_table(table)
+    rows = np.arange(n)[:, None]
+    inside = (idx >= 0) & (idx // chunk_size == rows // chunk_size)
+    total = float(w[idx >= 0].astype(np.float64).sum())
+    st["cut_weight_fraction"] = (1.0 - float(w[inside].astype(np.float64).sum()) / total) if total > 0 else 0.0
+    st["k_used"] = k
+    return order, st
+
+
 def count_pillars(ptr, ind, height, ncols=None):
     """Distinct (row // height, column) pairs (sporder/src/count_pillars.cu:38-85)."""
     ptr, ind = _i32(ptr), _i32(ind)

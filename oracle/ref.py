@@ -120,3 +120,18 @@ def similarity_graph(ptr, ind, is_symmetric=False, k=0, oversampling=0.0):
         C.c_float(oversampling), C.c_void_p(idx.data_ptr()), C.c_void_p(wgt.data_ptr()), None, None)
     torch.cuda.synchronize()
     return idx, wgt
+
+
+def chunk_greedy(ptr, ind, is_symmetric=False, k=0, oversampling=0.0, chunk_size=0):
+    """sporder_chunk_greedy of the reference (sporder/include/sporder.h:176-182) on int32
+    CUDA torch tensors; returns the order tensor."""
+    import torch
+    n, nnz = ptr.numel() - 1, ind.numel()
+    order = torch.empty(n, dtype=torch.int32, device=ptr.device)
+    torch.cuda.synchronize()
+    lib().sporder_chunk_greedy(
+        _context(), C.c_int32(n), C.c_int32(nnz), C.c_void_p(ptr.data_ptr()),
+        C.c_void_p(ind.data_ptr()), C.c_bool(bool(is_symmetric)), C.c_int32(k),
+        C.c_float(oversampling), C.c_int32(chunk_size), C.c_void_p(order.data_ptr()), None, None)
+    torch.cuda.synchronize()
+    return order

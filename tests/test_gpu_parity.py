@@ -252,6 +252,24 @@ def test_similarity_graph_matches_oracle_and_reference(name):
             assert np.array_equal(r_wgt.cpu().numpy().view(np.uint32), o_wgt.view(np.uint32))
 
 
+@pytest.mark.parametrize("name", ["band1000", "ragged", "hubsym", "rmat12", "stencil48", "dense_ragged"])
+def test_chunk_greedy_on_the_global_graph(name):
+    from oracle import ref
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build(name)
+    d_ptr, d_ind = _dev(ptr), _dev(ind)
+    for kw in (dict(), dict(k=8, oversampling=4.0, chunk_size=100), dict(chunk_size=4096)):
+        order, stats = sp.chunk_greedy(d_ptr, d_ind, is_symmetric=sym, with_stats=True, **kw)
+        o_order, o_st = oracle.chunk_greedy(ptr, ind, **kw)
+        assert np.array_equal(order.cpu().numpy(), o_order)
+        assert stats["k_used"] == o_st["k_used"]
+        assert stats["chain_restarts"] == o_st["restarts"]
+        # a diagnostic made of two fp32-accumulated sums (cg/stats_collector.cu:66-72)
+        assert abs(stats["cut_weight_fraction"] - o_st["cut_weight_fraction"]) < 1e-5
+        if ref.available():
+            assert np.array_equal(ref.chunk_greedy(d_ptr, d_ind, sym, **kw).cpu().numpy(), o_order)
+
+
 def test_harness_method_modules():
     # the shapes the reference's own scripts call: reorder_bench/methods/sporder_csg.py:25-70
     # and spmm_bench/base.py:8-65
