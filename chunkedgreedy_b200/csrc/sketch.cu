@@ -757,6 +757,25 @@ struct RoundState {
   uint32_t fence_sink;           // see phase_fence
 };
 
+// Slot that holds key s, or -1.  With TAB from the key -> slot table of the chunk (one byte
+// per row); without it - chunks whose tables would not fit shared memory - by comparing s
+// with every slot's key (keys are unique in a sketch, empty slots hold -1).
+template <int CELLS, bool TAB>
+__device__ __forceinline__ int slot_of(const RoundState<CELLS> &st, const uint8_t *tab, int32_t cbase,
+                                       int32_t s) {
+  if (TAB) return static_cast<int>(tab[s - cbase]) - 1;
+  int q = -1;
+#pragma unroll
+  for (int i4 = 0; i4 < 8 * CELLS; ++i4) {
+    const int4 kk = reinterpret_cast<const int4 *>(st.key)[i4];
+    q = kk.x == s ? 4 * i4 : q;
+    q = kk.y == s ? 4 * i4 + 1 : q;
+    q = kk.z == s ? 4 * i4 + 2 : q;
+    q = kk.w == s ? 4 * i4 + 3 : q;
+  }
+  return q;
+}
+
 // Keeps the phases of a round apart in the instruction schedule.  Left alone, ptxas
 // interleaves the window look-up, the count and the limit look-ups, and the round takes
 // 1220 cycles; with a read of %clock between them (which it does not move code across, as
@@ -768,7 +787,7 @@ __device__ __forceinline__ void phase_fence(uint32_t &sink) {
 }
 
 // One round on a full sketch; returns the number of stream elements resolved (>= 1).
-template <int CELLS>
+template <int CELLS, bool TAB>
 __device__ __forceinline__ int round_full(RoundState<CELLS> &st, uint8_t *tab, int32_t cbase,
                                           const int2 *ring, int p, int cnt, int lane,
                                           uint32_t &sink) {
@@ -786,7 +805,7 @@ __device__ __forceinline__ int round_full(RoundState<CELLS> &st, uint8_t *tab, i
     mine[c] = st.w[c * 32 + lane];
     mykey[c] = st.key[c * 32 + lane];
   }
-  const int q = valid ? static_cast<int>(tab[s - cbase]) - 1 : 0;
+  const int q = valid ? slot_of<CELLS, TAB>(st, tab, cbase, s) : 0;
   const bool miss = valid && q < 0;
   const bool hit = valid && q >= 0;
   // lanes carrying the same key: a second miss of a key ends the prefix (1); hits of one
@@ -871,10 +890,10 @@ __device__ __forceinline__ int round_full(RoundState<CELLS> &st, uint8_t *tab, i
   if (times > 2)
     for (int t = 2; t < times; ++t) wv += al;
   if (applies && miss) {
-    tab[old_key - cbase] = 0;
+    if (TAB) tab[old_key - cbase] = 0;
     st.key[tgt] = s;
     st.w[tgt] = nb;
-    tab[s - cbase] = static_cast<uint8_t>(tgt + 1);
+    if (TAB) tab[s - cbase] = static_cast<uint8_t>(tgt + 1);
   }
   if (applies && hit && (mates & below) == 0u) st.w[q] = __float_as_uint(wv);  // first hit of its key
   __syncwarp();
@@ -882,7 +901,7 @@ __device__ __forceinline__ int round_full(RoundState<CELLS> &st, uint8_t *tab, i
 }
 
 // One round while the sketch has empty slots; `filled` is updated.
-template <int CELLS>
+template <int CELLS, bool TAB>
 __device__ __forceinline__ int round_fill(RoundState<CELLS> &st, uint8_t *tab, int32_t cbase,
                                           const int2 *ring, int p, int cnt, int lane,
                                           int &filled) {
@@ -892,7 +911,7 @@ __device__ __forceinline__ int round_fill(RoundState<CELLS> &st, uint8_t *tab, i
   const int2 elem = valid ? ring[p + lane] : make_int2(0, 0);
   const int32_t s = elem.x;
   const float al = __int_as_float(elem.y);
-  const int q = valid ? static_cast<int>(tab[s - cbase]) - 1 : 0;
+  const int q = valid ? slot_of<CELLS, TAB>(st, tab, cbase, s) : 0;
   const bool miss = valid && q < 0;
   const bool hit = valid && q >= 0;
   const uint32_t missing = __ballot_sync(FULL, miss);
@@ -908,7 +927,7 @@ __device__ __forceinline__ int round_fill(RoundState<CELLS> &st, uint8_t *tab, i
       const int code = (j % CELLS) * 32 + j / CELLS;
       st.key[code] = s;
       st.w[code] = __float_as_uint(al);
-      tab[s - cbase] = static_cast<uint8_t>(code + 1);
+      if (TAB) tab[s - cbase] = static_cast<uint8_t>(code + 1);
     } else if (hit && ((same & prefix) & below) == 0u) {
       float wv = __uint_as_float(st.w[q]);
       for (int t = __popc(same & prefix); t > 0; --t) wv += al;
@@ -935,7 +954,7 @@ __device__ __forceinline__ void stage_batch(int2 *ring, const int2 *in, int cnt,
 // One heavy row, start to finish: stream batches in, rounds, final sketch out.  Not
 // inlined: compiled as part of the kernel's ticket loop the same rounds take 1280 cycles
 // instead of 1000.
-template <int CELLS>
+template <int CELLS, bool TAB>
 __device__ __noinline__ void rounds_row(const int2 *in, uint32_t total, int32_t cbase,
                                         RoundState<CELLS> &st, uint8_t *tab, int2 *ring0, int2 *ring1,
                                         int32_t *out) {
@@ -961,8 +980,8 @@ __device__ __noinline__ void rounds_row(const int2 *in, uint32_t total, int32_t 
     __syncwarp();
     const int2 *ring = buf ? ring1 : ring0;
     int p = 0;
-    while (p < cnt && filled < M) p += round_fill<CELLS>(st, tab, cbase, ring, p, cnt, lane, filled);
-    while (p < cnt) p += round_full<CELLS>(st, tab, cbase, ring, p, cnt, lane, sink);
+    while (p < cnt && filled < M) p += round_fill<CELLS, TAB>(st, tab, cbase, ring, p, cnt, lane, filled);
+    while (p < cnt) p += round_full<CELLS, TAB>(st, tab, cbase, ring, p, cnt, lane, sink);
     buf ^= 1;
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -971,7 +990,7 @@ __device__ __noinline__ void rounds_row(const int2 *in, uint32_t total, int32_t 
     const int32_t kk = st.key[c * 32 + lane];
     out[(2 * c) * 32 + lane] = kk;
     out[(2 * c + 1) * 32 + lane] = static_cast<int32_t>(st.w[c * 32 + lane]);
-    if (kk >= 0) tab[kk - cbase] = 0;  // the table is empty again for the next row
+    if (TAB && kk >= 0) tab[kk - cbase] = 0;  // the table is empty again for the next row
   }
   if (lane == 0) st.fence_sink = sink;
   __syncwarp();
@@ -995,9 +1014,13 @@ __global__ void __launch_bounds__(S_THREADS, 1) heavy_rounds_kernel(SketchArgs a
     item = __shfl_sync(FULL, item, 0);
     if (item >= heavy) break;
     const int32_t r = a.row_list[item];
-    rounds_row<CELLS>(a.hstream + a.heavy_off[item], a.row_work[r], (r / a.chunk) * a.chunk, state[warp],
-                      tab, rings[warp][0], rings[warp][1],
-                      a.heavy_state + static_cast<size_t>(item) * (2 * CELLS * 32));
+    int32_t *out = a.heavy_state + static_cast<size_t>(item) * (2 * CELLS * 32);
+    if (tab_bytes > 0)
+      rounds_row<CELLS, true>(a.hstream + a.heavy_off[item], a.row_work[r], (r / a.chunk) * a.chunk,
+                              state[warp], tab, rings[warp][0], rings[warp][1], out);
+    else  // chunk too large for key tables in shared memory
+      rounds_row<CELLS, false>(a.hstream + a.heavy_off[item], a.row_work[r], 0, state[warp], nullptr,
+                               rings[warp][0], rings[warp][1], out);
   }
 }
 
@@ -1032,15 +1055,16 @@ bool launch_cells(Context &ctx, const SketchArgs &a) {
   heavy_expand_kernel<<<ctx.num_sms * 8, S_THREADS, 0, ctx.stream>>>(a);
   CSG_CUDA(cudaGetLastError());
   // The chain kernel asks for all the shared memory of an SM, so that it runs one block
-  // per SM.  Sketches of up to ROUND_CELLS cells per lane are resolved in rounds when the
-  // key tables of a block's four warps (one byte per row of a chunk each) fit in there.
+  // per SM.  Sketches of up to ROUND_CELLS cells per lane are resolved in rounds, with key
+  // tables for a block's four warps (one byte per row of a chunk each) when they fit in there.
   bool in_rounds = false;
   if constexpr (CELLS <= ROUND_CELLS) {
     cudaFuncAttributes fa;
     CSG_CUDA(cudaFuncGetAttributes(&fa, heavy_rounds_kernel<CELLS>));
     const int pad = ctx.smem_optin - 1024 - static_cast<int>(fa.sharedSizeBytes);
-    const int64_t tab_bytes = (static_cast<int64_t>(a.chunk) + 15) / 16 * 16;
-    if (ROUND_RING_BYTES + tab_bytes * S_WARPS <= pad) {
+    int64_t tab_bytes = (static_cast<int64_t>(a.chunk) + 15) / 16 * 16;
+    if (ROUND_RING_BYTES + tab_bytes * S_WARPS > pad) tab_bytes = 0;  // slots found by comparing keys
+    {
       CSG_CUDA(cudaFuncSetAttribute(heavy_rounds_kernel<CELLS>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, pad));
       heavy_rounds_kernel<CELLS><<<ctx.num_sms, S_THREADS, pad, ctx.stream>>>(a, static_cast<int>(tab_bytes));

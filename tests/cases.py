@@ -62,7 +62,7 @@ BIG_CASES = {
     # rows streaming more than 65536 candidates (the heavy-row path of the sketch stage):
     # equal Dice terms (weights tie all the time), fewer candidates than slots (the sketch
     # never fills), one cell per lane, unequal terms with noise, a 4096-row chunk, and a
-    # chunk too large for the key tables (element-wise chain)
+    # chunk too large for the key tables (slots found by comparing keys)
     "dense_ties": _case(lambda: synth.dense_block(1024, 0, 300, 300, 21), False, k=16),
     "dense_fill": _case(lambda: synth.dense_block(2048, 10, 40, 2000, 22), False, k=16),
     "dense_m32": _case(lambda: synth.dense_block(1024, 0, 200, 400, 23), False, k=8,
