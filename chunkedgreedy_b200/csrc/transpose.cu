@@ -396,12 +396,19 @@ __global__ void __launch_bounds__(256) heavy_scan_kernel(TransposeArgs a) {
   const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
   for (int32_t h = blockIdx.x; h < H; h += gridDim.x) {
     const int32_t t0 = a.heavy_tile_base[h], t1 = a.heavy_tile_base[h + 1];
+    // a chunk of millions of nonzeros has hundreds of tiles: sixteen loads in flight per
+    // thread, or the walk costs one memory latency per tile
     uint32_t run = 0;
-    for (int32_t t = t0; t < t1; ++t) {
-      uint32_t *cell = a.tile_hist + static_cast<size_t>(t) * 256 + d;
-      const uint32_t v = *cell;
-      *cell = run;
-      run += v;
+    for (int32_t tb = t0; tb < t1; tb += 16) {
+      uint32_t v[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+        v[u] = tb + u < t1 ? a.tile_hist[static_cast<size_t>(tb + u) * 256 + d] : 0u;
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        if (tb + u < t1) a.tile_hist[static_cast<size_t>(tb + u) * 256 + d] = run;
+        run += v[u];
+      }
     }
     uint32_t incl = run;
 #pragma unroll
