@@ -188,7 +188,7 @@ bool run_csg(Context &ctx, int32_t n, int32_t ncols, int32_t row_base, int32_t n
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[0], st));
   if (!launch_transpose(ctx, n, ncols, nnz, p.chunk, d_ptr, d_ind, s)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
-  if (!launch_sketch(ctx, n, nnz, p, d_ptr, s, row_base)) return false;
+  if (!launch_sketch(ctx, n, nnz, p, d_ptr, s, row_base, d_table != nullptr || stats != nullptr)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[2], st));
   if (stats && !launch_table_stats(ctx, n, p.k, s.table, s.ctrl)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[3], st));
@@ -271,7 +271,7 @@ bool run_similarity_graph(Context &ctx, int32_t n, int32_t nnz, const int32_t *d
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[0], st));
   if (!launch_transpose(ctx, n, n, nnz, p.chunk, d_ptr, d_ind, s)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
-  if (!launch_sketch(ctx, n, nnz, p, d_ptr, s, 0)) return false;
+  if (!launch_sketch(ctx, n, nnz, p, d_ptr, s, 0, true)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[2], st));
   if (stats && !launch_table_stats(ctx, n, p.k, s.table, s.ctrl)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[3], st));
@@ -334,7 +334,7 @@ bool run_chunk_greedy(Context &ctx, int32_t n, int32_t nnz, const int32_t *d_ptr
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[0], st));
   if (!launch_transpose(ctx, n, n, nnz, ps.chunk, d_ptr, d_ind, s)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
-  if (!launch_sketch(ctx, n, nnz, ps, d_ptr, s, 0)) return false;
+  if (!launch_sketch(ctx, n, nnz, ps, d_ptr, s, 0, stats != nullptr)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[2], st));
   if (stats) {
     if (!launch_table_stats(ctx, n, pg.k, s.table, s.ctrl)) return false;

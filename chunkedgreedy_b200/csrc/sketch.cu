@@ -254,7 +254,7 @@ struct Sketch {
     }
   }
 
-  // writes the valid prefix of the row's k entries (the table is pre-zeroed)
+  // writes the row's k entries: the valid prefix, then zeros
   __device__ __forceinline__ void select_top_k(int32_t k, uint64_t *out, int32_t row_base) {
     local_sort_descending();
     int pos = 0;
@@ -283,6 +283,7 @@ struct Sketch {
       }
     }
     if ((i & 31) != 0 && lane < (i & 31)) out[(i & ~31) + lane] = mine;
+    for (int j = i + lane; j < k; j += 32) out[j] = 0;  // the stages behind stop at the first empty entry
   }
 };
 
@@ -1106,7 +1107,7 @@ bool launch_cells(Context &ctx, const SketchArgs &a) {
 }  // namespace
 
 bool launch_sketch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, const int32_t *d_ptr,
-                   CsgScratch &s, int32_t row_base) {
+                   CsgScratch &s, int32_t row_base, bool zero_table) {
   SketchArgs a;
   a.n = n;
   a.nnz = nnz;
@@ -1128,8 +1129,11 @@ bool launch_sketch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, con
   a.part_off = s.part_off;
   a.ctrl = s.ctrl;
   a.table = s.table;
-  // rows without candidates are never visited: their entries must read as empty
-  CSG_CUDA(cudaMemsetAsync(s.table, 0, sizeof(uint64_t) * static_cast<size_t>(n) * p.k, ctx.stream));
+  // Rows without candidates are never visited.  The greedy stage knows them from their work
+  // count and never reads their entries; whoever reads the whole table (its export, the
+  // statistics) needs them to read as empty.
+  if (zero_table)
+    CSG_CUDA(cudaMemsetAsync(s.table, 0, sizeof(uint64_t) * static_cast<size_t>(n) * p.k, ctx.stream));
   switch (p.M / 32) {
 #define CSG_CASE(C) \
   case C:           \

@@ -78,13 +78,14 @@ def gather_shards(local, bounds, group=None):
 
 
 def csg_shard(ptr_local, ind_local, n_cols, row_base, *, k, oversampling=0.0, chunk_size=0,
-              with_table=False, with_timing=False, ctx=None):
+              with_table=False, with_timing=False, with_stats=False, ctx=None):
     """Reorder one row shard on the current CUDA device (``sporder_csg_shard``).
 
     ``ptr_local`` / ``ind_local``: int32 CUDA tensors of the block (pointers rebased to 0).
-    Returns the block's slice of the global permutation [, its table rows] [, timing]."""
+    Returns the block's slice of the global permutation [, its table rows] [, timing]
+    [, statistics of the block]."""
     import torch
-    from . import _ctx, _enter, _lib, _timing_dict
+    from . import _ctx, _enter, _lib, _stats_dict, _timing_dict
     n_rows, nnz = ptr_local.numel() - 1, ind_local.numel()
     if k <= 0:
         raise ValueError("csg_shard needs the matrix-wide k (see resolve_k)")
@@ -92,7 +93,7 @@ def csg_shard(ptr_local, ind_local, n_cols, row_base, *, k, oversampling=0.0, ch
     lib = _lib.load()
     order = torch.empty(max(n_rows, 0), dtype=torch.int32, device=ptr_local.device)
     table = torch.empty((n_rows, k), dtype=torch.int64, device=ptr_local.device) if with_table else None
-    timing = _lib.CsgTiming()
+    timing, stats = _lib.CsgTiming(), _lib.CsgStats()
     if n_rows > 0:
         with torch.cuda.device(ptr_local.device):
             _enter(ctx, ptr_local)
@@ -100,7 +101,8 @@ def csg_shard(ptr_local, ind_local, n_cols, row_base, *, k, oversampling=0.0, ch
                 ctx.handle, n_rows, int(n_cols), int(row_base), nnz, ptr_local.data_ptr(),
                 ind_local.data_ptr(), int(k), float(oversampling), int(chunk_size),
                 order.data_ptr(), table.data_ptr() if with_table else None,
-                table.numel() if with_table else 0, C.byref(timing) if with_timing else None, None)
+                table.numel() if with_table else 0, C.byref(timing) if with_timing else None,
+                C.byref(stats) if with_stats else None)
         if rc < 0:
             _lib.check()
     out = (order,)
@@ -108,6 +110,8 @@ def csg_shard(ptr_local, ind_local, n_cols, row_base, *, k, oversampling=0.0, ch
         out += (table,)
     if with_timing:
         out += (_timing_dict(timing),)
+    if with_stats:
+        out += (_stats_dict(stats),)
     return out if len(out) > 1 else out[0]
 
 
