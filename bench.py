@@ -202,6 +202,12 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     import oracle
+    # every core this process may run on: torchrun sets OMP_NUM_THREADS=1 for its ranks,
+    # which would time one thread of the CPU arm at N > 1
+    try:
+        oracle.set_num_threads(len(os.sched_getaffinity(0)))
+    except AttributeError:
+        oracle.set_num_threads(os.cpu_count() or 1)
     ptr, ind, _ = load_workload(args.scale, args.workload)
     n, nnz = ptr.size - 1, ind.size
     k = min(256, max(16, nnz // n))
@@ -366,6 +372,10 @@ def run_ours(args, rank, world, local_rank):
     }
     if world == 1 and not args.no_cpu_baseline:
         import oracle
+        try:
+            oracle.set_num_threads(len(os.sched_getaffinity(0)))
+        except AttributeError:
+            oracle.set_num_threads(os.cpu_count() or 1)
         step, sample_nnz, desc = cpu_reference_rate(ptr, ind, k, args.cpu_budget, 1)
         secs = step()
         line["cpu_baseline"] = {"value": sample_nnz / secs / 1e6, "unit": "Mnnz/s",
