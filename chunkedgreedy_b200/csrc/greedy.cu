@@ -105,21 +105,54 @@ __global__ void __launch_bounds__(G_WARPS * 32) greedy_kernel(GreedyArgs a) {
       cur = best_c;
       continue;
     }
-    // restart at the smallest unvisited row; `scan` only moves forward
+    // Restart at the smallest unvisited row; `scan` only moves forward.  A row without a
+    // list (no bit in `nonempty`) would be emitted, find no neighbour and restart again, one
+    // dependent step each - and on many inputs most rows are like that.  They change nothing
+    // for the rows behind them, so all unvisited rows without a list in front of the first
+    // unvisited row WITH a list are emitted here at once, in index order, as the chain
+    // would have emitted them one by one (each of them counts as one restart).
     int32_t nxt = -1;
     for (int32_t base = scan; base < words; base += 32) {
       const int32_t w = base + lane;
-      uint32_t fr = 0;
+      uint32_t fr = 0, ne = 0;
       if (w < words) {
         fr = ~visited[w];
         if (w == words - 1 && (size & 31)) fr &= (1u << (size & 31)) - 1u;
+        ne = nonempty[w];
       }
-      const unsigned m = __ballot_sync(FULL, fr != 0);
-      if (m) {
-        const int l = __ffs(m) - 1;
-        const uint32_t f = __shfl_sync(FULL, fr, l);
-        scan = base + l;
-        nxt = (scan << 5) + __ffs(f) - 1;
+      const uint32_t listed = fr & ne, bare = fr & ~ne;
+      const unsigned mb = __ballot_sync(FULL, listed != 0);
+      const int lb = mb ? __ffs(mb) - 1 : 32;  // lane of the first word that holds a row with a list
+      const uint32_t fb = __shfl_sync(FULL, listed, lb & 31);
+      const int bitb = mb ? __ffs(fb) - 1 : 0;
+      uint32_t take = lane < lb ? bare : (lane == lb ? bare & ((1u << bitb) - 1u) : 0u);
+      if (__any_sync(FULL, take != 0)) {
+        const int32_t cnt = __popc(take);
+        int32_t incl = cnt;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const int32_t t = __shfl_up_sync(FULL, incl, off);
+          if (lane >= off) incl += t;
+        }
+        const int32_t total = __shfl_sync(FULL, incl, 31);
+        // entries still waiting in registers go out first, then the run, in place
+        if (lane < (emitted & 31)) a.order[start + (emitted & ~31) + lane] = mine;
+        int32_t at = start + emitted + incl - cnt;
+        if (w < words) visited[w] |= take;
+        while (take) {
+          const int b = __ffs(take) - 1;
+          take &= take - 1;
+          a.order[at++] = start + (w << 5) + b + a.row_base;
+        }
+        emitted += total;
+        restarts += total;
+        __syncwarp();
+        // the block of 32 that is being filled now: its first entries are already in memory
+        if (lane < (emitted & 31)) mine = a.order[start + (emitted & ~31) + lane];
+      }
+      if (mb) {
+        scan = base + lb;
+        nxt = (scan << 5) + bitb;
         break;
       }
     }
