@@ -85,6 +85,10 @@ __global__ void __launch_bounds__(G_WARPS * 32) greedy_kernel(GreedyArgs a) {
         if (cand < start || cand >= end) continue;
         const int32_t cl = cand - start;
         if (visited[cl >> 5] & (1u << (cl & 31))) continue;
+        // The next row of the chain is one of these candidates, and its list is needed as
+        // soon as the arg-max below is known: ask for every candidate's list now, so that the
+        // one dependent load per step finds it in L1 instead of waiting on L2.
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(a.table + static_cast<size_t>(cand) * a.k));
         const uint32_t wb = entry_weight_bits(e);
         if (wb > best_w || (wb == best_w && cand < best_c)) {
           best_w = wb;
