@@ -17,6 +17,13 @@ region).  With N > 1 (launched under torchrun) the rows are cut into N chunk-ali
 shards, one per GPU, and the permutation shards are all-gathered with NCCL; the total
 work is fixed, so scaling is "strong".
 
+With N > 1 the post-reorder SpMM is row-partitioned as well (nonzero-balanced row ranges, the
+dense operand replicated on every GPU, each GPU owning its rows of the result) and timed as the
+maximum over ranks.  Every line carries `parity`: the permutation the timed calls produced,
+compared with the CPU restatement (on a sample of whole chunks at every N, on the whole matrix
+where the CPU leg runs it) and with the reference's own CUDA library, plus its SHA-256 so that
+the lines of different N can be compared.
+
 `--impl reference` times the CPU restatement of the reference's algorithm (the
 reference has no CPU implementation of csg; its own code is CUDA) on the host cores,
 each step on a bounded sample of whole chunks of the same matrix.
@@ -90,11 +97,11 @@ def load_workload(scale, name="rmat22"):
 def chunk_sample(ptr, ind, fraction, chunk=CHUNK):
     """A bounded sample of the workload made of whole chunks: chunks are sorted by their
     nonzero count and every (1/fraction)-th is taken, so light and heavy chunks appear in
-    proportion.  Returns a CSR block (rows renumbered, columns kept) and its nnz."""
+    proportion.  Returns a CSR block (rows renumbered, columns kept) and the chunks taken."""
     n = ptr.size - 1
     nch = (n + chunk - 1) // chunk
     if fraction >= 1.0:
-        return ptr, ind, nch
+        return ptr, ind, np.arange(nch)
     edges = np.minimum(np.arange(nch + 1, dtype=np.int64) * chunk, n)
     cnt = np.diff(ptr[edges].astype(np.int64))
     order = np.argsort(-cnt, kind="stable")
@@ -109,13 +116,24 @@ def chunk_sample(ptr, ind, fraction, chunk=CHUNK):
         pieces_ind.append(ind[b:e])
         base += e - b
     return (np.concatenate(pieces_ptr).astype(np.int32),
-            np.concatenate(pieces_ind) if pieces_ind else np.zeros(0, np.int32), len(take))
+            np.concatenate(pieces_ind) if pieces_ind else np.zeros(0, np.int32), take)
+
+
+def sample_matches(order_full, sample_order, take, n, chunk=CHUNK):
+    """True when the permutation of the whole matrix, restricted to the sampled chunks, is
+    the permutation computed for the sample (chunks are independent problems: chunk j of the
+    sample is chunk take[j] of the matrix with its rows renumbered)."""
+    for j, q in enumerate(take):
+        r0, r1 = int(q) * chunk, min((int(q) + 1) * chunk, n)
+        if not np.array_equal(order_full[r0:r1] - r0, sample_order[j * chunk:j * chunk + (r1 - r0)] - j * chunk):
+            return False
+    return True
 
 
 def cpu_reference_rate(ptr, ind, k, budget_s, steps_total, threads=None):
     """Times the CPU restatement (oracle/) on a sample sized so that `steps_total` steps
     fit in about `budget_s` seconds.  Returns (callable running one step -> seconds,
-    sample nnz, description)."""
+    sample nnz, description, chunks of the sample, holder of the last step's permutation)."""
     import oracle
     if threads:
         oracle.set_num_threads(threads)
@@ -128,17 +146,18 @@ def cpu_reference_rate(ptr, ind, k, budget_s, steps_total, threads=None):
     rate = max(pi.size, 1) / max(probe, 1e-6)  # nnz / s
     want = rate * budget_s / max(steps_total, 1)
     fraction = min(1.0, max(1.0 / 64, want / max(ind.size, 1)))
-    sp_, si_, sc = chunk_sample(ptr, ind, fraction)
+    sp_, si_, take = chunk_sample(ptr, ind, fraction)
+    last = {}
 
     def step():
         t = time.perf_counter()
-        oracle.csg(sp_, si_, False, k=k, ncols=n)
+        last["order"] = oracle.csg(sp_, si_, False, k=k, ncols=n)
         return time.perf_counter() - t
 
     nch = (n + CHUNK - 1) // CHUNK
     desc = "%d of %d chunks (every %d-th by nonzero count), %d nnz, full csg per step" % (
-        sc, nch, max(1, int(round(1.0 / fraction))), si_.size)
-    return step, int(si_.size), desc
+        len(take), nch, max(1, int(round(1.0 / fraction))), si_.size)
+    return step, int(si_.size), desc, take, last
 
 
 class ClockSampler:
@@ -211,8 +230,8 @@ def run_reference(args, rank, world):
     ptr, ind, _ = load_workload(args.scale, args.workload)
     n, nnz = ptr.size - 1, ind.size
     k = min(256, max(16, nnz // n))
-    step, sample_nnz, desc = cpu_reference_rate(ptr, ind, k, args.cpu_budget,
-                                                args.steps + args.warmup)
+    step, sample_nnz, desc, _, _ = cpu_reference_rate(ptr, ind, k, args.cpu_budget,
+                                                      args.steps + args.warmup)
     for _ in range(args.warmup):
         step()
     total = sum(step() for _ in range(args.steps))
@@ -334,6 +353,11 @@ def run_ours(args, rank, world, local_rank):
     e2e_value = nnz * args.steps / float(e2e_s.item()) / 1e6
 
     log("e2e done")
+    # ---- post-reorder SpMM (every rank takes part: row-partitioned at N > 1) ----------
+    spmm = None
+    if not args.no_spmm:
+        spmm = spmm_section(sp, ctx, ptr, ind, val, order, n, nnz, dev, world, rank,
+                            t_ms / args.steps, with_reference=(world == 1 and not args.no_ref_cuda))
     if rank != 0:
         return
     peaks = {}
@@ -343,14 +367,17 @@ def run_ours(args, rank, world, local_rank):
         pass
     hbm = float(peaks.get("hbm_gbs", 6650.0))
     peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
-    # algorithmic bytes of the sketch/top-k stage of THIS rank's shard: the pattern read
-    # once row-wise and once in transposed view, the table written once -- the k entries of
-    # every row that has a candidate; rows without one are known from the transpose and never
-    # touched (one untimed call with statistics counts them)
+    # Algorithmic bytes of the sketch/top-k stage of THIS rank's shard: the pattern read once
+    # row-wise and once in transposed view, the table written once.  Two counts: with k
+    # entries for every row, and with the entries of the rows that have a candidate only
+    # (rows without one are known from the transpose and never touched; one untimed call
+    # with statistics counts them).  The fraction uses the narrower, lower count.
     _, st_loc = csgdist.csg_shard(d_ptr, d_ind, n, r0, k=k, chunk_size=CHUNK, ctx=ctx, with_stats=True)
     rows_written = n_loc - int(st_loc["zero_degree_rows"])
     b_sketch = 2 * (4 * (n_loc + 1) + 4 * nnz_loc) + 8 * rows_written * k
+    b_sketch_all_rows = 2 * (4 * (n_loc + 1) + 4 * nnz_loc) + 8 * n_loc * k
     ach = b_sketch / (stage["sketch_ms"] * 1e-3) / 1e9 if stage["sketch_ms"] > 0 else 0.0
+    order_np = order.cpu().numpy()
     line = {
         "metric": "csg reorder throughput", "value": value, "unit": "Mnnz/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_ms / args.steps,
@@ -368,91 +395,266 @@ def run_ours(args, rank, world, local_rank):
                      "achieved": ach,
                      "peak": hbm, "unit": "GB/s", "frac": ach / hbm, "peak_source": peak_src,
                      "algorithmic_bytes": int(b_sketch), "table_rows_written": int(rows_written),
-                     "traffic": TRAFFIC_FROM_NCU.get(args.workload if args.scale == 22 else None)},
+                     "algorithmic_bytes_all_rows": int(b_sketch_all_rows),
+                     "frac_all_rows": (b_sketch_all_rows / (stage["sketch_ms"] * 1e-3) / 1e9 / hbm
+                                       if stage["sketch_ms"] > 0 else 0.0),
+                     "traffic": None, "traffic_note": TRAFFIC_NOTE},
+        "parity": parity_section(order_np, ptr, ind, k, n),
     }
+    if world == 1 and args.workload == "rmat22" and args.scale == 22:
+        line["roofline"]["traffic"] = TRAFFIC_RMAT22
     if world == 1 and not args.no_cpu_baseline:
         import oracle
         try:
             oracle.set_num_threads(len(os.sched_getaffinity(0)))
         except AttributeError:
             oracle.set_num_threads(os.cpu_count() or 1)
-        step, sample_nnz, desc = cpu_reference_rate(ptr, ind, k, args.cpu_budget, 1)
+        step, sample_nnz, desc, take, last = cpu_reference_rate(ptr, ind, k, args.cpu_budget, 1)
         secs = step()
         line["cpu_baseline"] = {"value": sample_nnz / secs / 1e6, "unit": "Mnnz/s",
                                 "cores": oracle.num_threads(), "kind": "port", "sample": desc}
+        line["parity"]["vs_oracle"] = bool(sample_matches(order_np, last["order"], take, n))
+        line["parity"]["vs_oracle_scope"] = desc
         log("cpu baseline done")
     if world == 1 and not args.no_ref_cuda:
         from chunkedgreedy_b200 import synth
-        line["reference_cuda"] = reference_cuda(d_ptr, d_ind, nnz, synth.WORKLOADS[args.workload][2])
+        sym = synth.WORKLOADS[args.workload][2]
+        line["reference_cuda"], ref_order = reference_cuda(d_ptr, d_ind, nnz, sym)
+        if ref_order is not None:
+            line["parity"]["vs_reference_cuda"] = bool(np.array_equal(ref_order.cpu().numpy(), order_np))
+        # the same protocol for this library: one untimed call, a flushed L2, then the
+        # library's own wall_ms and stage times (reorder_bench/methods/sporder_csg.py:41-57)
+        line["same_protocol"] = same_protocol_pair(sp, ctx, d_ptr, d_ind, sym, line["reference_cuda"])
         log("reference cuda done", line["reference_cuda"])
-    if world == 1 and not args.no_spmm:
-        line["spmm"] = spmm_section(sp, ctx, d_ptr, d_ind, torch.from_numpy(val).to(dev), order,
-                                    n, nnz, hbm)
-        line["pillars_h16"] = line["spmm"].pop("pillars_h16")
+    if spmm is not None:
+        line["pillars_h16"] = spmm.pop("pillars_h16", None)
+        line["apply"] = spmm.pop("apply", None)
+        line["spmm"] = spmm
     if world == 1 and args.gcn:
         line["gcn"] = gcn_section(d_ptr, d_ind, torch.from_numpy(val).to(dev), n, ctx,
                                   args.gcn_epochs)
+    if world == 1 and not args.no_configs and args.workload == "rmat22":
+        line["configs"] = other_configs(sp, ctx, dev, args.configs_budget)
     emit(line)
 
 
-# DRAM bytes (read + write) of the sketch stage's kernels per csg call, from an ncu capture
-# of this command at full size (profiles/sketch_stage_rmat22_dram_traffic.md)
-TRAFFIC_FROM_NCU = {"rmat22": 4558039552}
+# DRAM bytes (read + write) of the sketch stage's kernels per csg call at full size, from an
+# ncu capture of `bench.py --steps 1 --warmup 1 --no-ref-cuda --no-cpu-baseline --no-spmm`;
+# a number of the build it was captured on, not of this run
+TRAFFIC_RMAT22 = 4558039552
+TRAFFIC_NOTE = ("dram__bytes_read+write of heavy_expand + heavy_rounds + sketch_kernel + heavy_topk, "
+                "one ncu capture at N=1 on the scale-22 matrix; null for other sizes and N")
+
+
+def order_digest(order_np):
+    import hashlib
+    return hashlib.sha256(np.ascontiguousarray(order_np, dtype=np.int32).tobytes()).hexdigest()
+
+
+def parity_section(order_np, ptr, ind, k, n):
+    """What every line can say about the permutation the timed calls produced: its digest
+    (equal across N when the row shards reproduce the single-GPU answer), the structural
+    invariants of a csg order (a permutation; every chunk a permutation of its own rows that
+    starts at the chunk's first row, sporder/src/csg/chunk_similarity_greedy.cu:31), and a
+    comparison with the CPU restatement on 1/64 of the chunks."""
+    import oracle
+    out = {"order_sha256": order_digest(order_np)}
+    full = (n // CHUNK) * CHUNK
+    blocks = order_np[:full].reshape(-1, CHUNK).astype(np.int64)
+    ok = bool(np.array_equal(blocks[:, 0], np.arange(0, full, CHUNK)))
+    ok = ok and bool(np.array_equal(np.sort(blocks, axis=1), np.arange(full).reshape(-1, CHUNK)))
+    if n > full:
+        ok = ok and bool(np.array_equal(np.sort(order_np[full:]), np.arange(full, n)))
+    out["structure_ok"] = ok
+    try:
+        oracle.set_num_threads(len(os.sched_getaffinity(0)))
+    except AttributeError:
+        pass
+    sp_, si_, take = chunk_sample(ptr, ind, 1.0 / 64)
+    want = oracle.csg(sp_, si_, False, k=k, ncols=n)
+    out["vs_oracle_sample"] = bool(sample_matches(order_np, want, take, n))
+    out["vs_oracle_sample_scope"] = "%d chunks (every 64-th by nonzero count)" % len(take)
+    return out
 
 
 def reference_cuda(d_ptr, d_ind, nnz, is_symmetric=False):
     """The reference's own CUDA library, built unchanged for sm_100a (oracle/_ref), on the
     same matrix with its benchmark protocol (one warm-up call, then the library's wall_ms;
-    bench/reorder/reorder_bench/methods/sporder_csg.py:41-57)."""
+    bench/reorder/reorder_bench/methods/sporder_csg.py:41-57).  Returns (record, order)."""
     try:
         from oracle import ref
         if not ref.available():
-            return {"unavailable": "oracle/_ref/libsporder_ref.so not present"}
+            return {"unavailable": "oracle/_ref/libsporder_ref.so not present"}, None
         import torch
         ref.csg(d_ptr, d_ind, is_symmetric)
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=d_ptr.device)
         flush.zero_()
-        _, tm = ref.csg(d_ptr, d_ind, is_symmetric, with_timing=True)
+        order, tm = ref.csg(d_ptr, d_ind, is_symmetric, with_timing=True)
+        torch.cuda.synchronize()
         return {"value": nnz / (tm["wall_ms"] * 1e-3) / 1e6, "unit": "Mnnz/s", "timing_ms": tm,
-                "kind": "reference CUDA sources compiled for sm_100a, 1 GPU"}
+                "stage_sum_ms": tm["csr2csc_ms"] + tm["similarity_ms"] + tm["chunk_greedy_ms"],
+                "kind": "reference CUDA sources compiled for sm_100a, 1 GPU"}, order
     except Exception as e:  # never let the comparison leg break the bench line
+        return {"unavailable": repr(e)[:200]}, None
+
+
+def same_protocol_pair(sp, ctx, d_ptr, d_ind, is_symmetric, ref_record):
+    """This library under the reference harness's protocol, beside the reference's numbers
+    taken the same way: wall_ms of the second call after an L2 flush, and the stage sums."""
+    import torch
+    try:
+        sp.chunk_similarity_greedy(d_ptr, d_ind, is_symmetric=is_symmetric, ctx=ctx)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=d_ptr.device)
+        flush.zero_()
+        torch.cuda.synchronize()
+        _, tm = sp.chunk_similarity_greedy(d_ptr, d_ind, is_symmetric=is_symmetric, with_timing=True,
+                                           ctx=ctx)
+        ours_sum = tm["csr2csc_ms"] + tm["similarity_ms"] + tm["chunk_greedy_ms"]
+        out = {"ours_wall_ms": tm["wall_ms"], "ours_stage_sum_ms": ours_sum}
+        if "timing_ms" in ref_record:
+            out["reference_wall_ms"] = ref_record["timing_ms"]["wall_ms"]
+            out["reference_stage_sum_ms"] = ref_record["stage_sum_ms"]
+            out["wall_ratio"] = out["reference_wall_ms"] / tm["wall_ms"]
+            out["stage_sum_ratio"] = out["reference_stage_sum_ms"] / ours_sum if ours_sum > 0 else None
+        return out
+    except Exception as e:
         return {"unavailable": repr(e)[:200]}
 
 
-def spmm_section(sp, ctx, d_ptr, d_ind, d_val, order, n, nnz, hbm, widths=(32, 128)):
-    """Post-reorder SpMM: GFLOP/s = 2*nnz*w / t (spmatkit/spmatkit.py:2150-2155) on
-    A' = P A P^T and on A, with the library's fp32 kernel."""
+def _time_launches(fn, warm=3, reps=10):
     import torch
+    for _ in range(warm):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def spmm_section(sp, ctx, ptr, ind, val, order, n, nnz, dev, world, rank, reorder_ms,
+                 with_reference=False, widths=(32, 128, 256)):
+    """Post-reorder SpMM: GFLOP/s = 2*nnz*w / t (spmatkit/spmatkit.py:2150-2155) on
+    A' = P A P^T and on A with the library's fp32 kernel; at N > 1 row-partitioned
+    (nonzero-balanced row ranges, dense operand replicated, results left sharded) and timed
+    as the maximum over ranks.  Also: the symmetric permutation apply itself, the reference's
+    quality metric before and after, cuSPARSE CSR_ALG1 on the same patterns through the
+    reference's own timer (sporder/src/bench_cusparse_spmm.cu:64-90), and the number of
+    launches that amortise the reorder (bench/spmm/scripts/compute_amortization.py:63-66)."""
+    import torch
+    import torch.distributed as dist
+    from chunkedgreedy_b200 import dist as csgdist
+    from chunkedgreedy_b200 import harness
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
     out = {}
+    d_ptr = torch.from_numpy(ptr).to(dev)
+    d_ind = torch.from_numpy(ind).to(dev)
+    d_val = torch.from_numpy(val).to(dev)
     p2, i2, v2 = sp.reorder(d_ptr, d_ind, order, val=d_val, symmetric=True, ctx=ctx)
-    # the reference's quality metric (configs/paper.yaml:30-32: distinct columns per window of
-    # 16 rows, fewer is better) before and after the reorder
-    t0 = time.perf_counter()
-    before = sp.count_pillars(d_ptr, d_ind, 16, ctx=ctx)
-    ms = (time.perf_counter() - t0) * 1e3
-    out["pillars_h16"] = {"original": before, "reordered": sp.count_pillars(p2, i2, 16, ctx=ctx),
-                          "count_ms": ms}
+    if rank == 0:
+        # the permutation apply: B_apply = 2*4(n+1) + 2*4n + 2*8*nnz (read and write ptr, the
+        # permutation and its inverse, indices and values once each)
+        ms = _time_launches(lambda: sp.reorder(d_ptr, d_ind, order, val=d_val, symmetric=True, ctx=ctx),
+                            warm=1, reps=3)
+        b_apply = 2 * 4 * (n + 1) + 2 * 4 * n + 2 * 8 * nnz
+        out["apply"] = {"ours_ms": ms, "algorithmic_bytes": int(b_apply),
+                        "roofline_frac": b_apply / (ms * 1e-3) / 1e9 / hbm, "mode": "symmetric, with values"}
+        if with_reference:
+            try:
+                from oracle import ref
+                if ref.available():
+                    rp, ri, rv = ref.reorder(d_ptr, d_ind, order, val=d_val, symmetric=True)
+                    torch.cuda.synchronize()
+                    out["apply"]["matches_reference"] = bool(
+                        torch.equal(rp, p2) and torch.equal(ri, i2) and torch.equal(rv, v2))
+                    t0 = time.perf_counter()
+                    for _ in range(3):
+                        ref.reorder(d_ptr, d_ind, order, val=d_val, symmetric=True)
+                    torch.cuda.synchronize()
+                    out["apply"]["reference_ms"] = (time.perf_counter() - t0) * 1e3 / 3
+                    del rp, ri, rv
+            except Exception as e:
+                out["apply"]["reference_unavailable"] = repr(e)[:200]
+        # the reference's quality metric (configs/paper.yaml:30-32: distinct columns per
+        # window of 16 rows, fewer is better) before and after the reorder
+        t0 = time.perf_counter()
+        before = sp.count_pillars(d_ptr, d_ind, 16, ctx=ctx)
+        ms = (time.perf_counter() - t0) * 1e3
+        out["pillars_h16"] = {"original": before, "reordered": sp.count_pillars(p2, i2, 16, ctx=ctx),
+                              "count_ms": ms}
+    mats = (("original", (d_ptr, d_ind, d_val)), ("reordered", (p2, i2, v2)))
+    bounds = {tag: csgdist.spmm_row_bounds(m[0], world) for tag, m in mats}
     for w in widths:
-        B = torch.randn((n, w), device=d_ptr.device, dtype=torch.float32)
-        C = torch.empty_like(B)
+        B = torch.randn((n, w), device=dev, dtype=torch.float32)
         res = {}
-        for tag, (pp, ii, vv) in (("original", (d_ptr, d_ind, d_val)), ("reordered", (p2, i2, v2))):
-            for _ in range(3):
-                sp.spmm(pp, ii, vv, B, out=C, ctx=ctx, sync=False)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            reps = 10
-            e0.record()
-            for _ in range(reps):
-                sp.spmm(pp, ii, vv, B, out=C, ctx=ctx, sync=False)
-            e1.record()
-            torch.cuda.synchronize()
-            ms = e0.elapsed_time(e1) / reps
+        for tag, (pp, ii, vv) in mats:
+            r0, r1 = bounds[tag][rank]
+            pl, il, vl = csgdist.spmm_shard(pp, ii, vv, r0, r1) if world > 1 else (pp, ii, vv)
+            C = torch.empty((max(r1 - r0, 1), w), device=dev, dtype=torch.float32)
+            if r1 > r0:
+                ms = _time_launches(lambda: sp.spmm(pl, il, vl, B, out=C[: r1 - r0], n_cols=n, ctx=ctx,
+                                                    sync=False))
+            else:
+                ms = 0.0
+            t = torch.tensor([ms], device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
             algo = 4 * (n + 1) + 8 * nnz + 8 * n * w  # pattern + values once, B and C once
             res[tag] = {"ms": ms, "gflops": 2.0 * nnz * w / (ms * 1e6),
-                        "roofline_frac": algo / (ms * 1e-3) / 1e9 / hbm}
+                        "roofline_frac": algo / (ms * 1e-3) / 1e9 / hbm,
+                        "gather_bytes_frac": (4.0 * nnz * w + 8 * nnz + 4 * n * w) / (ms * 1e-3) / 1e9 / hbm}
+            if with_reference and rank == 0:
+                try:
+                    from oracle import ref
+                    if ref.available():
+                        res[tag]["cusparse_ms"] = ref.cusparse_spmm(pp, ii, w, warmup=3, repeat=10)
+                except Exception as e:
+                    res[tag]["cusparse_unavailable"] = repr(e)[:200]
+            del C
         res["speedup"] = res["original"]["ms"] / res["reordered"]["ms"]
+        res["amortization_runs"] = harness.format_amortization(
+            harness.amortization_runs(reorder_ms, res["original"]["ms"], res["reordered"]["ms"]))
         out["w%d" % w] = res
-        del B, C
+        del B
+    out["partition"] = ("one GPU" if world == 1 else
+                        "rows cut into %d nonzero-balanced ranges, dense operand replicated, "
+                        "result left sharded; ms = max over ranks" % world)
+    return out
+
+
+def other_configs(sp, ctx, dev, budget_s):
+    """The remaining benchmark configurations at full size, within a time budget: csg
+    throughput, stage times and the digest of the permutation for each."""
+    import torch
+    from chunkedgreedy_b200 import synth
+    out, t_begin = {}, time.time()
+    for name in ("zipf65k", "stencil1024", "road2m", "rmat20gcn"):
+        if time.time() - t_begin > budget_s:
+            out[name] = {"skipped": "time budget of %.0f s used up" % budget_s}
+            continue
+        try:
+            ptr, ind, _ = load_workload(0, name)
+            sym = synth.WORKLOADS[name][2]
+            d_ptr, d_ind = torch.from_numpy(ptr).to(dev), torch.from_numpy(ind).to(dev)
+            n, nnz = ptr.size - 1, ind.size
+            ms = _time_launches(lambda: sp.chunk_similarity_greedy(d_ptr, d_ind, is_symmetric=sym, ctx=ctx),
+                                warm=2, reps=5)
+            order, tm = sp.chunk_similarity_greedy(d_ptr, d_ind, is_symmetric=sym, with_timing=True, ctx=ctx)
+            out[name] = {"n": int(n), "nnz": int(nnz), "ms": ms, "Mnnz_per_s": nnz / (ms * 1e-3) / 1e6,
+                         "stages_ms": {"transpose_ms": tm["csr2csc_ms"], "sketch_ms": tm["similarity_ms"],
+                                       "greedy_ms": tm["chunk_greedy_ms"]},
+                         "order_sha256": order_digest(order.cpu().numpy())}
+            del d_ptr, d_ind
+        except Exception as e:
+            out[name] = {"failed": repr(e)[:200]}
     return out
 
 
@@ -467,6 +669,9 @@ def gcn_section(d_ptr, d_ind, d_val, n, ctx, epochs):
     r = gcn.reorder_and_train(d_ptr, d_ind, d_val, x, y, hidden=128, classes=16, epochs=epochs,
                               optimizer="sgd", ctx=ctx)
     r.pop("order")
+    for key, v in list(r.items()):  # JSON has no infinity: the harness's text form instead
+        if isinstance(v, float) and (v == float("inf") or v != v):
+            r[key] = "inf" if v == float("inf") else "nan"
     return r
 
 
@@ -506,6 +711,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref-cuda", action="store_true")
     ap.add_argument("--no-spmm", action="store_true")
+    ap.add_argument("--no-configs", action="store_true",
+                    help="skip the short runs of the other benchmark configurations")
+    ap.add_argument("--configs-budget", type=float, default=90.0,
+                    help="seconds the runs of the other configurations may take (generation included)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -8,7 +8,9 @@ requested), permutations in new2old form.  Use it as
 ``import chunkedgreedy_b200 as sporder``.
 
 Arrays are CUDA tensors (``torch.Tensor``) or any object that exports DLPack /
-``__cuda_array_interface__``; results come back as torch tensors on the same
+``__cuda_array_interface__``; results come back in the framework of the first
+array argument (torch tensors for torch input; ``<framework>.from_dlpack`` of the
+result otherwise, as in sporder/python/sporder/__init__.py:28-39), on the same
 device.  All work is done by hand-written sm_100a kernels behind the C ABI in
 ``include/sporder_b200.h``; there is no CPU fallback.
 """
@@ -32,18 +34,21 @@ def _torch():
 
 class Context:
     """Owns a CUDA stream and a device workspace, bound to the device current at
-    creation (sporder/include/sporder.h:43-52).  One context per thread or device."""
+    creation, or to ``device`` when given (sporder/include/sporder.h:43-52).  One context
+    per thread or device; a context serves one stream at a time (re-binding it to another
+    stream first waits for the work it queued on the previous one)."""
 
-    def __init__(self):
+    def __init__(self, device=None):
         torch = _torch()
         if not torch.cuda.is_available():
             raise RuntimeError("chunkedgreedy_b200 needs a CUDA device (no CPU fallback)")
         lib = _lib.load()
         torch.cuda.init()
-        self.device = torch.cuda.current_device()
-        # make sure the primary context exists before the library asks for the device
-        torch.empty(1, device="cuda")
-        self._h = lib.sporder_context_create()
+        self.device = torch.cuda.current_device() if device is None else int(device)
+        with torch.cuda.device(self.device):
+            # make sure the primary context exists before the library asks for the device
+            torch.empty(1, device="cuda")
+            self._h = lib.sporder_context_create()
         if not self._h:
             _lib.check()
             raise RuntimeError("sporder_context_create failed")
@@ -67,14 +72,37 @@ class Context:
             pass
 
 
-def _ctx(ctx):
+def _ctx(ctx, ref=None):
+    """The caller's context, or the shared default context of the device the arrays live on
+    (created on first use; sporder/python/bindings.cpp:40-43 keeps one such singleton)."""
     if ctx is not None:
         return ctx
     torch = _torch()
-    dev = torch.cuda.current_device()
-    if dev not in _default_ctx:  # shared default context, created on first use
-        _default_ctx[dev] = Context()
+    dev = ref.device.index if ref is not None and ref.is_cuda else torch.cuda.current_device()
+    if dev is None:
+        dev = torch.cuda.current_device()
+    if dev not in _default_ctx:
+        _default_ctx[dev] = Context(device=dev)
     return _default_ctx[dev]
+
+
+def _like(result, reference):
+    """``result`` (a torch tensor) in the array framework ``reference`` came from
+    (sporder/python/sporder/__init__.py:28-39): torch stays torch, any other framework that
+    offers ``from_dlpack`` (CuPy, ...) receives a zero-copy view."""
+    torch = _torch()
+    if result is None or isinstance(reference, torch.Tensor):
+        return result
+    root = type(reference).__module__.partition(".")[0]
+    if root in ("torch", "builtins", "numpy", ""):
+        return result
+    try:
+        import importlib
+        mod = importlib.import_module(root)
+    except Exception:
+        return result
+    conv = getattr(mod, "from_dlpack", None)
+    return conv(result) if conv is not None else result
 
 
 def _as_tensor(a, dtype, name):
@@ -127,10 +155,11 @@ def chunk_similarity_greedy(ptr, ind, *, is_symmetric=False, k=0, oversampling=0
     avg_degree, avg_edge_weight, zero_degree_rows, chunk_size_used, chain_restarts,
     avg_followed_weight) are appended when requested."""
     torch = _torch()
+    src = ptr
     ptr = _as_tensor(ptr, torch.int32, "ptr")
     ind = _as_tensor(ind, torch.int32, "ind")
     n, nnz = _sizes(ptr, ind)
-    ctx = _ctx(ctx)
+    ctx = _ctx(ctx, ptr)
     lib = _lib.load()
     with torch.cuda.device(ptr.device):
         _enter(ctx, ptr)
@@ -143,7 +172,7 @@ def chunk_similarity_greedy(ptr, ind, *, is_symmetric=False, k=0, oversampling=0
     msg = _lib.last_error()
     if msg:
         raise ValueError(msg) if "expect" in msg or "must be" in msg else RuntimeError(msg)
-    result = (order,)
+    result = (_like(order, src),)
     if with_timing:
         result += (_timing_dict(timing),)
     if with_stats:
@@ -158,10 +187,11 @@ def csg_table(ptr, ind, *, is_symmetric=False, k=0, oversampling=0.0, chunk_size
     of the weight, low word = index + 1, 0 = empty).  No reference counterpart: the
     reference never exposes this table."""
     torch = _torch()
+    src = ptr
     ptr = _as_tensor(ptr, torch.int32, "ptr")
     ind = _as_tensor(ind, torch.int32, "ind")
     n, nnz = _sizes(ptr, ind)
-    ctx = _ctx(ctx)
+    ctx = _ctx(ctx, ptr)
     lib = _lib.load()
     kk = int(k) if k > 0 else min(256, max(16, nnz // n))
     with torch.cuda.device(ptr.device):
@@ -176,7 +206,7 @@ def csg_table(ptr, ind, *, is_symmetric=False, k=0, oversampling=0.0, chunk_size
     if msg:
         raise ValueError(msg) if "expect" in msg or "must be" in msg else RuntimeError(msg)
     assert k_used == kk
-    return order, table
+    return _like(order, src), _like(table, src)
 
 
 def chunk_similarity_greedy_host(ptr, ind, *, is_symmetric=False, k=0, oversampling=0.0,
@@ -188,7 +218,7 @@ def chunk_similarity_greedy_host(ptr, ind, *, is_symmetric=False, k=0, oversampl
     if ptr.is_cuda or ind.is_cuda or ptr.dtype != torch.int32 or ind.dtype != torch.int32:
         raise ValueError("ptr and ind must be int32 host tensors")
     n, nnz = _sizes(ptr, ind)
-    ctx = _ctx(ctx)
+    ctx = _ctx(ctx, ptr)
     if out is None:
         out = torch.empty(n, dtype=torch.int32).pin_memory()
     lib = _lib.load()
@@ -207,10 +237,11 @@ def chunk_greedy(ptr, ind, *, is_symmetric=False, k=0, oversampling=0.0, chunk_s
     sporder/include/sporder.h:169-182): ``new_order`` [, timing dict] [, stats dict with
     the csg fields plus ``cut_weight_fraction``]."""
     torch = _torch()
+    src = ptr
     ptr = _as_tensor(ptr, torch.int32, "ptr")
     ind = _as_tensor(ind, torch.int32, "ind")
     n, nnz = _sizes(ptr, ind)
-    ctx = _ctx(ctx)
+    ctx = _ctx(ctx, ptr)
     lib = _lib.load()
     with torch.cuda.device(ptr.device):
         _enter(ctx, ptr)
@@ -223,7 +254,7 @@ def chunk_greedy(ptr, ind, *, is_symmetric=False, k=0, oversampling=0.0, chunk_s
     msg = _lib.last_error()
     if msg:
         raise ValueError(msg) if "expect" in msg or "must be" in msg else RuntimeError(msg)
-    result = (order,)
+    result = (_like(order, src),)
     if with_timing:
         result += (_timing_dict(timing),)
     if with_stats:
@@ -239,11 +270,12 @@ def similarity_graph(ptr, ind, *, is_symmetric=False, k=0, oversampling=0.0, wit
     (wall_ms, csr2csc_ms, similarity_ms, unpack_ms) and/or a ``stats`` dict (k_used, m_used,
     avg_degree, avg_edge_weight, zero_degree_rows) are appended when requested."""
     torch = _torch()
+    src = ptr
     ptr = _as_tensor(ptr, torch.int32, "ptr")
     ind = _as_tensor(ind, torch.int32, "ind")
     n, nnz = _sizes(ptr, ind)
     kk = int(k) if k > 0 else min(32, max(16, 2 * (nnz // max(n, 1))))  # sporder.cpp:75-77
-    ctx = _ctx(ctx)
+    ctx = _ctx(ctx, ptr)
     lib = _lib.load()
     with torch.cuda.device(ptr.device):
         _enter(ctx, ptr)
@@ -257,7 +289,7 @@ def similarity_graph(ptr, ind, *, is_symmetric=False, k=0, oversampling=0.0, wit
     if rc < 0:
         msg = _lib.last_error() or "sporder_similarity_graph failed"
         raise ValueError(msg) if "expect" in msg or "must be" in msg else RuntimeError(msg)
-    result = (idx, wgt)
+    result = (_like(idx, src), _like(wgt, src))
     if with_timing:
         result += (dict(wall_ms=timing.wall_ms, csr2csc_ms=timing.csr2csc_ms,
                         similarity_ms=timing.similarity_ms, unpack_ms=timing.unpack_ms),)
@@ -272,12 +304,13 @@ def count_pillars(ptr, ind, height, *, ctx=None):
     """Distinct (row // height, column) pairs of a CSR pattern: the reference's reordering
     quality metric, fewer is better (sporder/python/sporder/__init__.py:152-172)."""
     torch = _torch()
+    src = ptr
     ptr = _as_tensor(ptr, torch.int32, "ptr")
     ind = _as_tensor(ind, torch.int32, "ind")
     n, nnz = _sizes(ptr, ind)
     if int(height) < 1:
         raise ValueError("height must be >= 1")
-    ctx = _ctx(ctx)
+    ctx = _ctx(ctx, ptr)
     lib = _lib.load()
     out = C.c_int32(0)
     with torch.cuda.device(ptr.device):
@@ -293,6 +326,7 @@ def reorder(ptr, ind, new_order, *, val=None, symmetric=False, ctx=None):
     (sporder/python/sporder/__init__.py:113-149).  Returns ``(ptr_new, ind_new)`` or
     ``(ptr_new, ind_new, val_new)``; column indices are sorted inside each row."""
     torch = _torch()
+    src = ptr
     ptr = _as_tensor(ptr, torch.int32, "ptr")
     ind = _as_tensor(ind, torch.int32, "ind")
     new_order = _as_tensor(new_order, torch.int32, "new_order")
@@ -305,7 +339,7 @@ def reorder(ptr, ind, new_order, *, val=None, symmetric=False, ctx=None):
             raise ValueError("val must live on the same device as ptr")
         if val.numel() != nnz:
             raise ValueError("val must have length nnz")
-    ctx = _ctx(ctx)
+    ctx = _ctx(ctx, ptr)
     lib = _lib.load()
     with torch.cuda.device(ptr.device):
         _enter(ctx, ptr)
@@ -319,24 +353,31 @@ def reorder(ptr, ind, new_order, *, val=None, symmetric=False, ctx=None):
                             1 if symmetric else 0, ptr_new.data_ptr(), ind_new.data_ptr(),
                             val_new.data_ptr() if val is not None else None)
     _lib.check()
-    return (ptr_new, ind_new) if val is None else (ptr_new, ind_new, val_new)
+    out = (ptr_new, ind_new) if val is None else (ptr_new, ind_new, val_new)
+    return tuple(_like(a, src) for a in out)
 
 
-def spmm(ptr, ind, val, B, *, out=None, sync=True, ctx=None):
+def spmm(ptr, ind, val, B, *, out=None, sync=True, ctx=None, n_cols=None):
     """fp32 CSR SpMM ``C = A @ B`` with ``B`` a row-major ``(n, w)`` float32 CUDA
     tensor.  The reference has no first-party SpMM (it times third-party kernels,
     bench/spmm/spmm_bench/base.py:48-59); this is the kernel the reordered matrix is
-    fed to.  ``sync=False`` skips the final stream synchronisation."""
+    fed to.  ``sync=False`` skips the final stream synchronisation.  ``n_cols`` names the
+    column count of a row block cut out of a wider matrix (the row-partitioned multi-GPU
+    product): ``B`` then has ``n_cols`` rows and ``C`` as many rows as the block."""
     torch = _torch()
+    src = ptr
     ptr = _as_tensor(ptr, torch.int32, "ptr")
     ind = _as_tensor(ind, torch.int32, "ind")
     val = _as_tensor(val, torch.float32, "val")
     n, nnz = _sizes(ptr, ind)
-    if B.dim() != 2 or B.shape[0] != n or B.dtype != torch.float32 or not B.is_cuda:
-        raise ValueError("B must be a float32 CUDA tensor of shape (n, w)")
+    if not isinstance(B, torch.Tensor):
+        B = torch.from_dlpack(B)
+    rows_b = n if n_cols is None else int(n_cols)
+    if B.dim() != 2 or B.shape[0] != rows_b or B.dtype != torch.float32 or not B.is_cuda:
+        raise ValueError("B must be a float32 CUDA tensor of shape (%d, w)" % rows_b)
     B = B.contiguous()
     w = B.shape[1]
-    ctx = _ctx(ctx)
+    ctx = _ctx(ctx, ptr)
     lib = _lib.load()
     with torch.cuda.device(ptr.device):
         _enter(ctx, ptr)
@@ -347,7 +388,7 @@ def spmm(ptr, ind, val, B, *, out=None, sync=True, ctx=None):
                 B.data_ptr(), out.data_ptr())
     if rc != 0:
         _lib.check()
-    return out
+    return _like(out, src)
 
 
 def kernel_launches():

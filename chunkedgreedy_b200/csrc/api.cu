@@ -97,9 +97,28 @@ size_t greedy_bitmap_words(int32_t n, int32_t chunk) {
   return chunks * 2 * words;
 }
 
-// Lays out the scratch of one csg call in the context workspace.
+constexpr uint64_t STREAM_CAP_MAX = uint64_t(1) << 27;  // 2^27 elements = 1 GiB
+
+// Stream elements the buffer of the heaviest rows gets for this call: never more than the
+// rows could stream at all (nnz * chunk span), than 1 GiB or than the caller's limit; at
+// least what the largest earlier call of the context asked for, and for a first call eight
+// elements per nonzero (at least 2^20: 8 MiB).
+uint64_t stream_capacity(const Context &ctx, size_t nnz, size_t span) {
+  uint64_t cap = static_cast<uint64_t>(nnz) * 8;
+  if (cap < (uint64_t(1) << 20)) cap = uint64_t(1) << 20;
+  const uint64_t seen = ctx.stream_need_seen + (ctx.stream_need_seen >> 3);
+  if (cap < seen) cap = seen;
+  const uint64_t most = static_cast<uint64_t>(nnz) * span;
+  if (cap > most) cap = most;
+  if (cap > STREAM_CAP_MAX) cap = STREAM_CAP_MAX;
+  if (ctx.stream_limit && cap > ctx.stream_limit) cap = ctx.stream_limit;
+  return cap < 1 ? 1 : cap;
+}
+
+// Lays out the scratch of one csg call in the context workspace.  `transpose_only` leaves
+// out everything behind the chunk-local transpose (the pillar count needs no more).
 bool plan_scratch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, uint64_t *user_table,
-                  CsgScratch *s, int32_t greedy_chunk = 0) {
+                  CsgScratch *s, int32_t greedy_chunk = 0, bool transpose_only = false) {
   Arena ar;
   const size_t z = static_cast<size_t>(nnz > 0 ? nnz : 1);
   const size_t o_keyA = ar.take(4 * z), o_keyB = ar.take(4 * z);
@@ -109,7 +128,7 @@ bool plan_scratch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, uint
   const size_t o_list = ar.take(4 * static_cast<size_t>(n));
   const size_t o_ctrl = ar.take(4 * CTRL_WORDS);
   // (the greedy stage may run with another chunk size than the sketch: chunk_greedy)
-  size_t bw = greedy_bitmap_words(n, p.chunk);
+  size_t bw = transpose_only ? 0 : greedy_bitmap_words(n, p.chunk);
   if (greedy_chunk > 0 && greedy_bitmap_words(n, greedy_chunk) > bw) bw = greedy_bitmap_words(n, greedy_chunk);
   const size_t o_bm = ar.take(4 * (bw ? bw : 1));
   // heavy chunks hold more than 15360 nonzeros each and are cut into tiles of 4096
@@ -119,16 +138,15 @@ bool plan_scratch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, uint
   const size_t tiles_max = z / 4096 + heavy_max + 1;
   const size_t o_hc = ar.take(4 * heavy_max), o_htb = ar.take(4 * (heavy_max + 1));
   const size_t o_th = ar.take(4 * 256 * tiles_max), o_db = ar.take(4 * 256 * heavy_max);
-  // streams of the heaviest rows: at most 2^27 entries (1 GiB), less for small inputs
+  // streams of the heaviest rows
   const size_t span = static_cast<size_t>(p.chunk < n ? p.chunk : n);
-  size_t cap = z * span;
-  if (cap > (size_t(1) << 27)) cap = size_t(1) << 27;
+  const size_t cap = transpose_only ? 1 : static_cast<size_t>(stream_capacity(ctx, z, span));
   const size_t hmax = cap / (size_t(1) << (SKETCH_HEAVY_BUCKET - 1)) + 1;
   const size_t o_hs = ar.take(8 * cap), o_ho = ar.take(4 * (hmax + 1));
   const size_t o_hst = ar.take(4 * hmax * 2 * (p.M / 32) * 32);
-  const size_t pmax = z / SKETCH_PART_COLS + hmax + 1;  // column slices of the heavy rows
+  const size_t pmax = transpose_only ? 1 : z / SKETCH_PART_COLS + hmax + 1;  // column slices of the heavy rows
   const size_t o_pb = ar.take(4 * (hmax + 2)), o_po = ar.take(4 * (pmax + 1));
-  const size_t o_table = user_table ? 0 : ar.take(8 * static_cast<size_t>(n) * p.k);
+  const size_t o_table = (user_table || transpose_only) ? 0 : ar.take(8 * static_cast<size_t>(n) * p.k);
   if (!ensure_workspace(ctx, ar.off)) return false;
   s->keyA = reinterpret_cast<uint32_t *>(ctx.ws + o_keyA);
   s->keyB = reinterpret_cast<uint32_t *>(ctx.ws + o_keyB);
@@ -156,6 +174,24 @@ bool plan_scratch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, uint
   return true;
 }
 
+// End of a call that ran the transpose (and possibly the sketch): the control words come
+// back with the call's one synchronisation.  Malformed input and a refused stream slice are
+// errors; the stream need of the heavy rows is remembered for the context's next call.
+bool finish_call(Context &ctx, const CsgScratch &s) {
+  uint32_t *h = reinterpret_cast<uint32_t *>(ctx.h_pinned);
+  CSG_CUDA(cudaMemcpyAsync(h, s.ctrl, 16 * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx.stream));
+  CSG_CUDA(cudaStreamSynchronize(ctx.stream));
+  CSG_CUDA(cudaGetLastError());
+  CSG_REQUIRE(h[CTRL_BAD_INPUT] == 0,
+              "malformed CSR: row pointers must be non-decreasing inside [0, nnz] (results unspecified)");
+  CSG_REQUIRE(h[CTRL_STREAM_OVERRUN] == 0,
+              "internal: a heavy row's stream slice did not fit its place in the stream buffer");
+  uint64_t need = (static_cast<uint64_t>(h[CTRL_HEAVY_NEED + 1]) << 32) | h[CTRL_HEAVY_NEED];
+  if (need > STREAM_CAP_MAX) need = STREAM_CAP_MAX;
+  if (need > ctx.stream_need_seen) ctx.stream_need_seen = need;
+  return true;
+}
+
 // The pipeline of sporder/src/csg/chunk_similarity_greedy.cu:100-138 with the
 // stages of this library: chunk-local transpose -> sketch/top-k -> greedy.
 bool run_csg(Context &ctx, int32_t n, int32_t ncols, int32_t row_base, int32_t nnz,
@@ -174,8 +210,11 @@ bool run_csg(Context &ctx, int32_t n, int32_t ncols, int32_t row_base, int32_t n
     stats->chunk_size_used = p.chunk;
   }
   CSG_REQUIRE(d_ptr && (d_ind || nnz == 0), "null CSR arrays");
-  CSG_REQUIRE(ncols >= n && row_base >= 0 && static_cast<int64_t>(row_base) + n <= 0x7FFFFFFF,
-              "row block [%d, %d + %d) does not fit %d columns", row_base, row_base, n, ncols);
+  CSG_REQUIRE(ncols >= n && row_base >= 0 && static_cast<int64_t>(row_base) + n <= ncols,
+              "row block [%d, %d + %d) does not lie inside a matrix of %d rows", row_base, row_base, n, ncols);
+  CSG_REQUIRE(row_base % p.chunk == 0,
+              "row_base %d is not a multiple of the chunk size %d: the block would not hold whole chunks",
+              row_base, p.chunk);
   CSG_REQUIRE(!d_table || table_capacity >= static_cast<uint64_t>(n) * p.k,
               "table buffer holds %llu entries, need n * k = %llu",
               static_cast<unsigned long long>(table_capacity),
@@ -199,12 +238,7 @@ bool run_csg(Context &ctx, int32_t n, int32_t ncols, int32_t row_base, int32_t n
   ChainStatsHost hs;
   if (stats)
     CSG_CUDA(cudaMemcpyAsync(&hs, s.ctrl + CTRL_STATS, sizeof(hs), cudaMemcpyDeviceToHost, st));
-  CSG_CUDA(cudaMemcpyAsync(ctx.h_pinned, s.ctrl + CTRL_BAD_INPUT, sizeof(uint32_t),
-                           cudaMemcpyDeviceToHost, st));
-  CSG_CUDA(cudaStreamSynchronize(st));
-  CSG_CUDA(cudaGetLastError());
-  CSG_REQUIRE(ctx.h_pinned[0] == 0,
-              "malformed CSR: row pointers must be non-decreasing inside [0, nnz] (results unspecified)");
+  if (!finish_call(ctx, s)) return false;
   if (stats) {  // sporder/src/csg/stats_collector.cu:53-62
     stats->avg_degree = static_cast<double>(hs.total_degree) / n;
     stats->avg_edge_weight =
@@ -285,12 +319,7 @@ bool run_similarity_graph(Context &ctx, int32_t n, int32_t nnz, const int32_t *d
   ChainStatsHost hs;
   if (stats)
     CSG_CUDA(cudaMemcpyAsync(&hs, s.ctrl + CTRL_STATS, sizeof(hs), cudaMemcpyDeviceToHost, st));
-  CSG_CUDA(cudaMemcpyAsync(ctx.h_pinned, s.ctrl + CTRL_BAD_INPUT, sizeof(uint32_t),
-                           cudaMemcpyDeviceToHost, st));
-  CSG_CUDA(cudaStreamSynchronize(st));
-  CSG_CUDA(cudaGetLastError());
-  CSG_REQUIRE(ctx.h_pinned[0] == 0,
-              "malformed CSR: row pointers must be non-decreasing inside [0, nnz] (results unspecified)");
+  if (!finish_call(ctx, s)) return false;
   if (stats) {  // sporder/src/similarity_graph.cu:99-104
     stats->avg_degree = static_cast<double>(hs.total_degree) / n;
     stats->avg_edge_weight =
@@ -346,12 +375,7 @@ bool run_chunk_greedy(Context &ctx, int32_t n, int32_t nnz, const int32_t *d_ptr
   ChainStatsHost hs;
   if (stats)
     CSG_CUDA(cudaMemcpyAsync(&hs, s.ctrl + CTRL_STATS, sizeof(hs), cudaMemcpyDeviceToHost, st));
-  CSG_CUDA(cudaMemcpyAsync(ctx.h_pinned, s.ctrl + CTRL_BAD_INPUT, sizeof(uint32_t),
-                           cudaMemcpyDeviceToHost, st));
-  CSG_CUDA(cudaStreamSynchronize(st));
-  CSG_CUDA(cudaGetLastError());
-  CSG_REQUIRE(ctx.h_pinned[0] == 0,
-              "malformed CSR: row pointers must be non-decreasing inside [0, nnz] (results unspecified)");
+  if (!finish_call(ctx, s)) return false;
   if (stats) {  // sporder/src/cg/stats_collector.cu:52-73
     stats->avg_degree = static_cast<double>(hs.total_degree) / n;
     stats->avg_edge_weight =
@@ -401,7 +425,7 @@ bool run_count_pillars(Context &ctx, int32_t n, int32_t nnz, const int32_t *d_pt
     CsgParams p;
     if (!resolve_params(n, nnz, 1, 1.0f, height, &p)) return false;  // k = 1: smallest table the layout allows
     CsgScratch s;
-    if (!plan_scratch(ctx, n, nnz, p, nullptr, &s)) return false;
+    if (!plan_scratch(ctx, n, nnz, p, nullptr, &s, 0, true)) return false;
     if (!launch_transpose(ctx, n, n, nnz, p.chunk, d_ptr, d_ind, s)) return false;
     // the counter takes the place of the (now unused) sort buffer; the transpose set the flag word
     d_count = reinterpret_cast<unsigned long long *>(s.keyA);
@@ -467,7 +491,15 @@ void sporder_context_destroy(sporder_context_t h) {
 
 void sporder_context_set_stream(sporder_context_t h, void *stream) {
   if (!h) return;
-  h->c.stream = stream ? static_cast<cudaStream_t>(stream) : h->c.own_stream;  // see header
+  cudaStream_t next = stream ? static_cast<cudaStream_t>(stream) : h->c.own_stream;  // see header
+  // The workspace and its control words serve one stream at a time: work still queued on the
+  // previous stream (sporder_spmm_async) must be over before another stream may reuse them.
+  if (next != h->c.stream) cudaStreamSynchronize(h->c.stream);
+  h->c.stream = next;
+}
+
+void sporder_context_set_stream_limit(sporder_context_t h, uint64_t max_elements) {
+  if (h) h->c.stream_limit = max_elements;
 }
 
 uint64_t sporder_context_workspace_bytes(sporder_context_t h) { return h ? h->c.ws_bytes : 0; }

@@ -52,6 +52,13 @@ struct Context {
   int *h_pinned = nullptr;  // small pinned host buffer for counters (64 ints)
   char *stage = nullptr;    // device copies of host inputs (host-buffer entry point), kept between calls
   size_t stage_bytes = 0;
+  // Buffer for the materialised candidate streams of the heaviest rows (sketch.cu), in stream
+  // elements of 8 bytes.  A call starts from a size in proportion to its input; every call
+  // reports what all its heavy rows together would have needed, and the next call of the
+  // context plans that much (rows that do not fit are still computed, by the slower kernel of
+  // the light rows, so results never depend on the size).
+  uint64_t stream_need_seen = 0;   // largest need any call of this context reported
+  uint64_t stream_limit = 0;       // caller's upper bound (sporder_context_set_stream_limit), 0 = none
 };
 
 bool ensure_workspace(Context &ctx, size_t bytes);
@@ -109,6 +116,8 @@ enum {
   CTRL_HEAVY_ROWS = 6,     // rows at the head of row_list that the heavy sketch kernel takes
   CTRL_HEAVY_TICKET = 7,   // and the word after it: a second ticket
   CTRL_HEAVY_PARTS = 9,    // column slices of the heavy rows
+  CTRL_HEAVY_NEED = 10,    // and the word after it: stream elements of all rows of heavy weight (64-bit)
+  CTRL_STREAM_OVERRUN = 12,  // set by heavy_expand_kernel when a slice would pass the stream buffer
   CTRL_BUCKET_COUNT = 16,  // 33 entries
   CTRL_BUCKET_BASE = 56,   // 33 entries
   CTRL_BUCKET_FILL = 96,   // 33 entries
@@ -145,6 +154,14 @@ bool launch_spmm(Context &ctx, int32_t n, int32_t nnz, int32_t w, const int32_t 
 #ifdef __CUDACC__
 constexpr unsigned FULL = 0xFFFFFFFFu;
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
+
+// counter += v, sticking at 0xFFFFFFFF instead of wrapping.  Whoever sees the sum wrap puts
+// the ceiling back; the last operation on a counter that ever wrapped is such a repair, so
+// once all adders are done the counter reads 0xFFFFFFFF ("more than fits").
+__device__ __forceinline__ void saturating_add(uint32_t *counter, uint32_t v) {
+  const uint32_t old = atomicAdd(counter, v);
+  if (old + v < old) atomicMax(counter, 0xFFFFFFFFu);
+}
 
 // packed entry of the top-k table; wire format of the reference
 // (sporder/src/common/weighted_index.h:15-27): high word = fp32 bits of the

@@ -660,13 +660,21 @@ __global__ void __launch_bounds__(S_THREADS) heavy_expand_kernel(SketchArgs a) {
     if (part >= parts) break;
     const PartRef p = part_ref(a, part, heavy);
     if (p.pe <= p.pb) continue;
-    int2 *out = a.hstream + a.part_off[part];
+    uint32_t at = a.part_off[part];
+    int2 *out = a.hstream + at;
     prod.begin(p.r, p.pb, p.pe, p.row_size);
     for (;;) {
       const int cnt = prod.produce(bs, ba);
       if (cnt == 0) break;
+      // The offsets were laid out from the rows' work counters; a slice that would pass the
+      // end of the buffer all the same (counters and groups out of step) is refused, not written.
+      if (cnt > static_cast<int>(a.stream_cap) || at > a.stream_cap - static_cast<uint32_t>(cnt)) {
+        if (lane == 0) atomicExch(&a.ctrl[CTRL_STREAM_OVERRUN], 1u);
+        break;
+      }
       for (int i = lane; i < cnt; i += 32) out[i] = make_int2(bs[i], __float_as_int(ba[i]));
       out += cnt;
+      at += static_cast<uint32_t>(cnt);
       __syncwarp();
     }
   }

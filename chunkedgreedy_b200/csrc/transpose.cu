@@ -249,10 +249,12 @@ __device__ void emit_groups(const uint32_t *K, const PayT *P, uint32_t *S, PayT 
     a.seg[b + p] = make_int2(b + st, len);
     a.seg_rank[b + p] = i - st;
     if (len >= 2) {
+      // (a row's count can pass 32 bits when the chunk is the whole matrix: it sticks at the
+      // ceiling, which the sketch stage reads as "does not fit the stream buffer")
       if (rows_in_smem)
-        atomicAdd(&sh.row_work[row - cs], static_cast<uint32_t>(len - 1));
+        saturating_add(&sh.row_work[row - cs], static_cast<uint32_t>(len - 1));
       else
-        atomicAdd(&a.row_work[row], static_cast<uint32_t>(len - 1));
+        saturating_add(&a.row_work[row], static_cast<uint32_t>(len - 1));
     }
   }
 }
@@ -542,11 +544,11 @@ __global__ void __launch_bounds__(T_THREADS) heavy_emit_kernel(TransposeArgs a) 
         const int32_t lr = row_of(sptr, 0, r.rows, r.b + p);
         row = r.cs + lr;
         rl = sptr[lr + 1] - sptr[lr];
-        if (len >= 2) atomicAdd(&swork[lr], static_cast<uint32_t>(len - 1));
+        if (len >= 2) saturating_add(&swork[lr], static_cast<uint32_t>(len - 1));
       } else {
         row = row_of(a.ptr, r.cs, r.cs + r.rows, r.b + p);
         rl = a.ptr[row + 1] - a.ptr[row];
-        if (len >= 2) atomicAdd(&a.row_work[row], static_cast<uint32_t>(len - 1));
+        if (len >= 2) saturating_add(&a.row_work[row], static_cast<uint32_t>(len - 1));
       }
       a.cand[r.b + i] = make_int2(row, rl);
       a.seg[r.b + p] = make_int2(r.b + st, len);
@@ -555,7 +557,7 @@ __global__ void __launch_bounds__(T_THREADS) heavy_emit_kernel(TransposeArgs a) 
     if (staged) {
       __syncthreads();
       for (int32_t j = threadIdx.x; j < r.rows; j += T_THREADS)
-        if (swork[j]) atomicAdd(&a.row_work[r.cs + j], swork[j]);
+        if (swork[j]) saturating_add(&a.row_work[r.cs + j], swork[j]);
       __syncthreads();
     }
   }
@@ -565,15 +567,22 @@ __global__ void __launch_bounds__(T_THREADS) heavy_emit_kernel(TransposeArgs a) 
 __global__ void __launch_bounds__(256) bucket_count_kernel(int32_t n, const uint32_t *row_work,
                                                            uint32_t *ctrl) {
   __shared__ uint32_t bucket[33];
+  __shared__ unsigned long long need;
   if (threadIdx.x < 33) bucket[threadIdx.x] = 0;
+  if (threadIdx.x == 0) need = 0;
   __syncthreads();
   for (int32_t r = blockIdx.x * blockDim.x + threadIdx.x; r < n; r += gridDim.x * blockDim.x) {
     const uint32_t t = __ldcg(row_work + r);
     if (t) atomicAdd(&bucket[32 - __clz(t)], 1u);
+    // stream elements of the rows heavy enough for a materialised stream: what the stream
+    // buffer would have to hold for all of them (the host sizes the next call's buffer by it)
+    if (t >= (1u << (SKETCH_HEAVY_BUCKET - 1))) atomicAdd(&need, static_cast<unsigned long long>(t));
   }
   __syncthreads();
   if (threadIdx.x < 33 && bucket[threadIdx.x])
     atomicAdd(&ctrl[CTRL_BUCKET_COUNT + threadIdx.x], bucket[threadIdx.x]);
+  if (threadIdx.x == 0 && need)
+    atomicAdd(reinterpret_cast<unsigned long long *>(ctrl + CTRL_HEAVY_NEED), need);
 }
 
 // Heaviest bucket first: rows with 2^(b-1) <= work < 2^b sit in bucket b.

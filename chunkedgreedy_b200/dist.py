@@ -6,7 +6,11 @@ sporder/src/csg/chunk_similarity_greedy.cu:18-24), and the in-chunk part of ever
 list can be derived from the chunk's own rows.  A shard made of whole chunks therefore needs
 no data from other shards: each rank reorders its row block with the single-GPU kernels
 (``sporder_csg_shard``) and the only exchange is an all-gather of the permutation shards
-(4 bytes per row).  The reference has no multi-GPU mode; this module is new surface.
+(4 bytes per row).  The SpMM that follows the reorder shards by rows as well: every rank
+multiplies a contiguous, nonzero-balanced row range of the matrix with the whole dense
+operand (replicated) and owns that row range of the result; the result is all-gathered only
+when the next operation needs it whole (a GCN layer feeding the next propagation).  The
+reference has no multi-GPU mode; this module is new surface.
 
 Host logic here is backend-neutral (it runs under ``gloo`` on CPU in the tests with a
 stand-in for the per-shard compute); the product path calls the CUDA library.
@@ -18,7 +22,8 @@ import ctypes as C
 import numpy as np
 
 __all__ = ["shard_bounds", "extract_shard", "gather_shards", "csg_shard",
-           "chunk_similarity_greedy_sharded", "resolve_k"]
+           "chunk_similarity_greedy_sharded", "resolve_k", "spmm_row_bounds", "spmm_shard",
+           "spmm_sharded"]
 
 
 def resolve_k(n, nnz, k=0):
@@ -89,7 +94,7 @@ def csg_shard(ptr_local, ind_local, n_cols, row_base, *, k, oversampling=0.0, ch
     n_rows, nnz = ptr_local.numel() - 1, ind_local.numel()
     if k <= 0:
         raise ValueError("csg_shard needs the matrix-wide k (see resolve_k)")
-    ctx = _ctx(ctx)
+    ctx = _ctx(ctx, ptr_local)
     lib = _lib.load()
     order = torch.empty(max(n_rows, 0), dtype=torch.int32, device=ptr_local.device)
     table = torch.empty((n_rows, k), dtype=torch.int64, device=ptr_local.device) if with_table else None
@@ -139,3 +144,59 @@ def chunk_similarity_greedy_sharded(ptr, ind, *, k=0, oversampling=0.0, chunk_si
     else:
         local = compute(pl, il, n, r0, kk, oversampling, chunk)
     return gather_shards(local, bounds, group)
+
+
+def spmm_row_bounds(ptr, world_size):
+    """Contiguous row ranges ``[(r0, r1), ...]`` for the row-partitioned SpMM, one per rank,
+    balanced by nonzeros (no chunk alignment: SpMM rows are independent).  ``ptr`` may be a
+    numpy array or a (host or device) torch tensor."""
+    if hasattr(ptr, "detach"):
+        ptr = ptr.detach().cpu().numpy()
+    ptr = np.asarray(ptr)
+    n = ptr.size - 1
+    total = int(ptr[-1])
+    cuts = [0]
+    for r in range(1, world_size):
+        c = int(np.searchsorted(ptr, total * r / world_size, side="left"))
+        cuts.append(min(max(c, cuts[-1]), n))
+    cuts.append(n)
+    return [(cuts[i], cuts[i + 1]) for i in range(world_size)]
+
+
+def spmm_shard(ptr, ind, val, r0, r1):
+    """Rows ``[r0, r1)`` of a CSR matrix held in torch tensors as a CSR block: rebased row
+    pointers (a small new tensor) and views of the index and value arrays."""
+    b, e = int(ptr[r0]), int(ptr[r1])
+    return (ptr[r0:r1 + 1] - ptr[r0]).contiguous(), ind[b:e], val[b:e]
+
+
+def spmm_sharded(ptr, ind, val, B, *, bounds=None, gather=False, group=None, compute=None,
+                 out=None, ctx=None, sync=True):
+    """Row-partitioned ``C = A @ B`` over the ranks of ``group``: every rank holds the matrix
+    (``ptr``, ``ind``, ``val``: torch tensors, the SAME on every rank) and the whole dense
+    operand ``B``; it multiplies its own nonzero-balanced row range and returns that block of
+    ``C`` (shape ``(r1 - r0, w)``), or the whole ``C`` after one all-gather when
+    ``gather=True``.  No kernel ever reads another GPU's memory.
+
+    ``compute(ptr_local, ind_local, val_local, B) -> (rows, w) tensor`` replaces the CUDA
+    kernel (used by the CPU tests)."""
+    import torch
+    import torch.distributed as dist
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    if bounds is None:
+        bounds = spmm_row_bounds(ptr, world)
+    r0, r1 = bounds[rank]
+    w = B.shape[1]
+    if r1 > r0:
+        pl, il, vl = spmm_shard(ptr, ind, val, r0, r1)
+        if compute is None:
+            from . import spmm
+            local = spmm(pl, il, vl, B, n_cols=B.shape[0], out=out, ctx=ctx, sync=sync)
+        else:
+            local = compute(pl, il, vl, B)
+    else:
+        local = torch.empty((0, w), dtype=B.dtype, device=B.device)
+    if not gather:
+        return local
+    flat = gather_shards(local.reshape(-1), [(a * w, b * w) for a, b in bounds], group)
+    return flat.reshape(-1, w)

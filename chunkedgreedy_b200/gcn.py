@@ -22,7 +22,7 @@ import torch.nn.functional as F
 
 from . import chunk_similarity_greedy, reorder, spmm
 
-__all__ = ["SpMMFn", "GraphOperator", "GCN", "train", "reorder_and_train"]
+__all__ = ["SpMMFn", "GraphOperator", "GCN", "train", "reorder_and_train", "breakeven_epochs"]
 
 
 class SpMMFn(torch.autograd.Function):
@@ -117,6 +117,13 @@ def train(ptr, ind, val, x, y, *, hidden=128, classes=16, epochs=200, warmup=3, 
                 spmm_ms_per_epoch=spmm_ms / max(epochs, 1), final_loss=float(loss))
 
 
+def breakeven_epochs(reorder_ms, perm_ms, epoch_ms_original, epoch_ms_reordered):
+    """Epochs after which reordering has paid for itself: (reorder + permute) over the time
+    one epoch saves, infinite when an epoch did not get faster (analysis/e2e.py:32-33)."""
+    gain = float(epoch_ms_original) - float(epoch_ms_reordered)
+    return (float(reorder_ms) + float(perm_ms)) / gain if gain > 0 else float("inf")
+
+
 def reorder_and_train(ptr, ind, val, x, y, *, ctx=None, **kw):
     """The amortisation experiment: train on the matrix as given, then reorder once with
     csg, apply P A P^T to the matrix and P to features and labels, and train again.
@@ -137,4 +144,7 @@ def reorder_and_train(ptr, ind, val, x, y, *, ctx=None, **kw):
     return dict(original=base, reordered=re, reorder_ms=reorder_ms, perm_ms=perm_ms,
                 total_original_ms=base["train_ms"], total_reordered_ms=total_re,
                 epoch_speedup=base["epoch_ms"] / re["epoch_ms"],
+                spmm_speedup=(base["spmm_ms_per_epoch"] / re["spmm_ms_per_epoch"]
+                              if re["spmm_ms_per_epoch"] > 0 else float("nan")),
+                breakeven_epochs=breakeven_epochs(reorder_ms, perm_ms, base["epoch_ms"], re["epoch_ms"]),
                 end_to_end_speedup=base["train_ms"] / total_re, order=order)

@@ -17,7 +17,8 @@ from typing import Any
 
 import numpy as np
 
-__all__ = ["reorder", "ReorderResult", "prep_gpu", "flush_l2", "B200SpMM"]
+__all__ = ["reorder", "ReorderResult", "prep_gpu", "flush_l2", "B200SpMM", "amortization_runs",
+           "format_amortization"]
 
 
 try:  # the harness's own result type, when this runs inside the harness
@@ -41,7 +42,7 @@ def prep_gpu(csr, detect_symmetric=True, device=None):
     int32_max = np.iinfo(np.int32).max
     nrows, nnz = int(csr.shape[0]), int(csr.nnz)
     if nrows > int32_max or nnz > int32_max:
-        raise ValueError("sporder requires n and nnz within int32; got n=%d, nnz=%d" % (nrows, nnz))
+        raise ValueError("matrix does not fit 32-bit indices: %d rows, %d nonzeros" % (nrows, nnz))
     device = device or torch.device("cuda", torch.cuda.current_device())
     t0 = time.perf_counter()
     out = csr.copy()
@@ -83,6 +84,21 @@ def reorder(csr, params: dict[str, Any]) -> ReorderResult:
     return ReorderResult(row_perm=perm, reorder_time_ms=float(t["wall_ms"]), prep_time_ms=upload_ms,
                          perm_trans_ms=to_host_ms, timing_breakdown=stages,
                          effective_params={"is_symmetric": symmetric})
+
+
+def amortization_runs(reorder_time_ms, spmm_original_ms, spmm_reordered_ms):
+    """SpMM launches after which a reorder has paid for itself: reorder time over the time
+    one launch saves; infinite when the reordered matrix is not faster
+    (bench/spmm/scripts/compute_amortization.py:63-66)."""
+    saved = float(spmm_original_ms) - float(spmm_reordered_ms)
+    if saved <= 0:
+        return float("inf")
+    return float(reorder_time_ms) / saved
+
+
+def format_amortization(value):
+    """The harness's text form (compute_amortization.py:48-51): "inf" or ten significant digits."""
+    return "inf" if value == float("inf") else "%.10g" % value
 
 
 try:  # the harness's base class, when this runs inside the harness

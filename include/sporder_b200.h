@@ -165,8 +165,18 @@ SPORDER_API const char *sporder_last_error(void);
 
 /* Run the context's work on `stream` (a cudaStream_t) instead of the context's
  * private stream; NULL restores the private stream.  To name the legacy default
- * stream pass cudaStreamLegacy ((cudaStream_t)0x1), not 0.  Calls stay synchronous. */
+ * stream pass cudaStreamLegacy ((cudaStream_t)0x1), not 0.  Calls stay synchronous.
+ * A context serves one stream at a time: switching to another stream first waits for
+ * the work the context queued on the previous one (sporder_spmm_async). */
 SPORDER_API void sporder_context_set_stream(sporder_context_t ctx, void *stream);
+
+/* Upper bound, in stream elements of 8 bytes, on the buffer that holds the materialised
+ * candidate streams of the heaviest rows (rows that stream 65536 candidates or more are
+ * computed fastest from such a copy).  0 = no bound beyond the built-in 2^27 elements (1 GiB).
+ * Without a bound a call plans max(8 * nnz, 2^20) elements, or what the largest earlier
+ * call of this context needed, never more than nnz * chunk_size.  Rows that do not fit are
+ * computed by the kernel of the lighter rows; results are the same for every bound. */
+SPORDER_API void sporder_context_set_stream_limit(sporder_context_t ctx, uint64_t max_elements);
 
 /* Bytes of device workspace the context currently holds (grow-only cache). */
 SPORDER_API uint64_t sporder_context_workspace_bytes(sporder_context_t ctx);
@@ -206,7 +216,9 @@ SPORDER_API int32_t sporder_chunk_similarity_greedy_host(
     bool is_symmetric, int32_t k, float oversampling, int32_t chunk_size, int32_t *h_new_order,
     sporder_csg_timing_t *timing, sporder_csg_stats_t *stats);
 
-/* fp32 CSR SpMM: C[n x w] = A * B with B, C row-major (ld = w).  The reference
+/* fp32 CSR SpMM: C[n x w] = A * B with B, C row-major (ld = w).  n is the number of rows
+ * of A (and of C); B must hold a row for every column id in d_ind, so A may be a row block
+ * of a wider matrix (the row-partitioned multi-GPU product).  The reference
  * times third-party kernels (bench/spmm/spmm_bench/base.py:48-59) and cuSPARSE
  * (sporder/src/bench_cusparse_spmm.cu:64-90) here; it has no SpMM of its own.
  * Returns 0, or -1 on error. */
@@ -223,8 +235,8 @@ SPORDER_API int32_t sporder_spmm_async(sporder_context_t ctx, int32_t n, int32_t
 /* SpMM for callers that must not trigger a device allocation (no counterpart in the
  * reference).  Same product as sporder_spmm, but it takes no context and calls no
  * cudaMalloc / cudaFree or allocating routine: the queue of long rows sits in a fixed
- * 512 KiB array inside the library image (held by every GPU that loads the library
- * until the process exits).  Meant for hosts that gave all device memory to their own
+ * array of 512 KiB plus 256 bytes of counters inside the library image (held by every
+ * GPU that loads the library until the process exits).  Meant for hosts that gave all device memory to their own
  * pool, or that ban driver allocations on their request path because those stall the
  * whole device.
  *   - limit: nnz < 65536 * 1024 (67,108,864); larger inputs are rejected with an error;

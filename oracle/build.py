@@ -35,9 +35,20 @@ def build_oracle(force=False):
     return ORACLE_SO
 
 
-def build_ref(ref_root="/root/reference", force=False):
+def reference_root():
+    """Where the reference checkout lies: SPORDER_REFERENCE_ROOT, else the sibling directory
+    ``reference`` of this repository; None when neither holds the sporder sources."""
+    here_parent = os.path.dirname(os.path.dirname(HERE))
+    for cand in (os.environ.get("SPORDER_REFERENCE_ROOT"), os.path.join(here_parent, "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "sporder", "src")):
+            return cand
+    return None
+
+
+def build_ref(ref_root=None, force=False):
     """Compile the unmodified reference sources in place (needs ~4 min, no GPU)."""
-    if not os.path.isdir(os.path.join(ref_root, "sporder", "src")):
+    ref_root = ref_root or reference_root()
+    if not ref_root or not os.path.isdir(os.path.join(ref_root, "sporder", "src")):
         return REF_SO if os.path.exists(REF_SO) else None
     shim = os.path.join(HERE, "ref_shim.cu")
     if force or _stale(REF_SO, [shim, os.path.join(HERE, "build_ref.sh")]):

@@ -6,9 +6,13 @@
 # GPU parity tests and by bench.py as the "reference CUDA build on this box"
 # comparison, never by the product path.
 #
-# usage: oracle/build_ref.sh [reference_root]   (default /root/reference)
+# usage: oracle/build_ref.sh <reference_root>   (or SPORDER_REFERENCE_ROOT in the environment)
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:-${SPORDER_REFERENCE_ROOT:-}}"
+if [ -z "$REF" ]; then
+  echo "build_ref: no reference checkout named (argument or SPORDER_REFERENCE_ROOT); keeping prebuilt files" >&2
+  exit 0
+fi
 HERE="$(cd "$(dirname "$0")" && pwd)"
 OUT="$HERE/_ref"
 SP="$REF/sporder"

@@ -135,3 +135,20 @@ def chunk_greedy(ptr, ind, is_symmetric=False, k=0, oversampling=0.0, chunk_size
         C.c_float(oversampling), C.c_int32(chunk_size), C.c_void_p(order.data_ptr()), None, None)
     torch.cuda.synchronize()
     return order
+
+
+def cusparse_spmm(ptr, ind, cols, warmup=3, repeat=10, seed=7):
+    """sporder_bench_cusparse_spmm of the reference (sporder/include/sporder.h:295-299;
+    sporder/src/bench_cusparse_spmm.cu:64-90): cusparseSpMM(CSR_ALG1) on the pattern with
+    random fp32 values and a column-major dense operand of ``cols`` columns; returns the
+    average milliseconds per launch."""
+    import torch
+    n, nnz = ptr.numel() - 1, ind.numel()
+    ms = C.c_float(0.0)
+    torch.cuda.synchronize()
+    lib().sporder_bench_cusparse_spmm(
+        _context(), C.c_int32(n), C.c_int32(nnz), C.c_void_p(ptr.data_ptr()),
+        C.c_void_p(ind.data_ptr()), C.c_int32(int(cols)), C.c_int32(int(warmup)),
+        C.c_int32(int(repeat)), C.c_uint64(int(seed)), C.byref(ms))
+    torch.cuda.synchronize()
+    return float(ms.value)

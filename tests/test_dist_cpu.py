@@ -85,3 +85,55 @@ def test_gloo_sharded_csg_equals_single_process(world, name, tmp_path):
     mp.spawn(_worker, args=(world, _free_port(), name, path), nprocs=world, join=True)
     got = np.load(path)
     assert np.array_equal(got, oracle.csg(ptr, ind, False, **params))
+
+
+def test_spmm_row_bounds_cover_and_balance():
+    ptr, ind, val, sym, params = cases.build("zipf65k")
+    n = ptr.size - 1
+    for world in (1, 2, 3, 8):
+        b = csgdist.spmm_row_bounds(ptr, world)
+        assert len(b) == world and b[0][0] == 0 and b[-1][1] == n
+        assert all(a1 == b0 for (_, a1), (b0, _) in zip(b, b[1:]))
+        nnz = [int(ptr[r1] - ptr[r0]) for r0, r1 in b]
+        assert max(nnz) <= 1.2 * (sum(nnz) / world) + 4096
+    # more ranks than rows: the extra ranks get empty ranges
+    b = csgdist.spmm_row_bounds(np.array([0, 2, 3], dtype=np.int32), 5)
+    assert b[0][0] == 0 and b[-1][1] == 2 and sum(r1 - r0 for r0, r1 in b) == 2
+
+
+def _spmm_worker(rank, world, port, name, w, result_path):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ptr, ind, val, sym, params = cases.build(name)
+    n = ptr.size - 1
+    B = np.random.default_rng(5).standard_normal((n, w)).astype(np.float32)
+
+    def compute(pl, il, vl, Bt):  # the CPU restatement in place of the CUDA kernel
+        return torch.from_numpy(oracle.spmm_f32(pl.numpy(), il.numpy(), vl.numpy(), Bt.numpy()))
+
+    tp, ti, tv = torch.from_numpy(ptr), torch.from_numpy(ind), torch.from_numpy(val)
+    local = csgdist.spmm_sharded(tp, ti, tv, torch.from_numpy(B), compute=compute)
+    r0, r1 = csgdist.spmm_row_bounds(ptr, world)[rank]
+    assert tuple(local.shape) == (r1 - r0, w)
+    whole = csgdist.spmm_sharded(tp, ti, tv, torch.from_numpy(B), compute=compute, gather=True)
+    if rank == 0:
+        np.save(result_path, whole.numpy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,name,w", [(2, "rmat12", 8), (3, "ragged", 5), (2, "tiny1", 3)])
+def test_gloo_row_partitioned_spmm_equals_single_process(world, name, w, tmp_path):
+    import torch.multiprocessing as mp
+    ptr, ind, val, sym, params = cases.build(name)
+    n = ptr.size - 1
+    path = str(tmp_path / "c.npy")
+    mp.spawn(_spmm_worker, args=(world, _free_port(), name, w, path), nprocs=world, join=True)
+    B = np.random.default_rng(5).standard_normal((n, w)).astype(np.float32)
+    got = np.load(path)
+    assert got.shape == (n, w)
+    assert np.array_equal(got, oracle.spmm_f32(ptr, ind, val, B))  # same kernel, same order of adds
+    c64, cabs = oracle.spmm_f64(ptr, ind, val, B)
+    assert np.all(np.abs(got - c64) <= 1e-5 * cabs + 1e-30)

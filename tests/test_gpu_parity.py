@@ -55,7 +55,7 @@ def test_csg_larger_cases_against_oracle(name):
 
 @pytest.mark.parametrize("name", ["hubsym", "rmat12", "m512", "bigchunk", "rmat16", "dense_ties",
                                   "dense_fill", "dense_m32", "dense_ragged", "dense_m96",
-                                  "dense_m128", "dense_m128_ties"])
+                                  "dense_m128", "dense_m128_ties", "zipf65k"])
 def test_csg_against_reference_library(name):
     from oracle import ref
     if not ref.available():
@@ -156,12 +156,13 @@ def test_spmm_is_linear_and_permutation_consistent():
     assert torch.all((lhs - ax[order.long()]).abs() <= 1e-5 * scale[order.long()] + 1e-30)
 
 
-def test_stats_and_timing_fields():
+@pytest.mark.parametrize("name", ["rmat12", "hubsym", "ragged", "dense_ragged"])
+def test_stats_and_timing_fields(name):
     sp = _sp()
-    ptr, ind, val, sym, params = cases.build("rmat12")
+    ptr, ind, val, sym, params = cases.build(name)
     order, timing, stats = sp.chunk_similarity_greedy(_dev(ptr), _dev(ind), with_timing=True,
-                                                      with_stats=True)
-    o_or, s_or = oracle.csg(ptr, ind, sym, with_stats=True)
+                                                      with_stats=True, is_symmetric=sym, **params)
+    o_or, s_or = oracle.csg(ptr, ind, sym, with_stats=True, **params)
     assert np.array_equal(order.cpu().numpy(), o_or)
     assert set(timing) == {"wall_ms", "csr2csc_ms", "similarity_ms", "chunk_greedy_ms"}
     assert timing["wall_ms"] > 0
@@ -169,7 +170,7 @@ def test_stats_and_timing_fields():
         assert stats[key] == s_or[key], key
     for key in ("avg_degree", "avg_edge_weight", "avg_followed_weight"):
         assert abs(stats[key] - s_or[key]) <= 1e-6 * max(1.0, abs(s_or[key])), key
-    only_stats = sp.chunk_similarity_greedy(_dev(ptr), _dev(ind), with_stats=True)
+    only_stats = sp.chunk_similarity_greedy(_dev(ptr), _dev(ind), with_stats=True, **params)
     assert isinstance(only_stats, tuple) and len(only_stats) == 2 and "k_used" in only_stats[1]
 
 
@@ -379,6 +380,132 @@ def test_full_size_power_law_workload_properties():
     assert torch.equal(p3, dp) and torch.equal(i3, di) and torch.equal(v3, dv)
 
 
+
+def test_full_size_gcn_workload_bit_exact():
+    # benchmark configuration 5 at full size: R-MAT scale 20 symmetrised with self loops,
+    # k = nnz / n = 30, 128 slots (four cells per lane, the widest sketch resolved in rounds)
+    sp = _sp()
+    from chunkedgreedy_b200 import synth
+    w = synth.make_workload("rmat20gcn")
+    order = sp.chunk_similarity_greedy(_dev(w["ptr"]), _dev(w["ind"]), is_symmetric=True)
+    assert np.array_equal(order.cpu().numpy(), oracle.csg(w["ptr"], w["ind"], True))
+
+
+def test_heavy_rows_that_do_not_fit_the_stream_buffer_take_the_light_path():
+    # The heaviest rows are computed from a materialised copy of their candidate stream; rows
+    # whose copy does not fit the buffer go through the kernel of the lighter rows instead.
+    # A context limited to 100,000 stream elements keeps one row of this case (89,700
+    # candidates each) on the fast path and sends 299 back; no limit keeps all 300.
+    sp = _sp()
+    from chunkedgreedy_b200 import _lib
+    lib = _lib.load()
+    for name, limit in (("dense_ties", 100_000), ("dense_ragged", 150_000), ("dense_m128", 70_000),
+                        ("dense_ties", 1000)):
+        ptr, ind, val, sym, params = cases.build(name)
+        o_or, t_or = oracle.csg(ptr, ind, sym, with_table=True, **params)
+        ctx = sp.Context()
+        lib.sporder_context_set_stream_limit(ctx.handle, limit)
+        for _ in range(2):  # the second call plans from what the first one reported
+            order, table = sp.csg_table(_dev(ptr), _dev(ind), ctx=ctx, **params)
+            assert np.array_equal(table.cpu().numpy().view(np.uint64), t_or), (name, limit)
+            assert np.array_equal(order.cpu().numpy(), o_or), (name, limit)
+        lib.sporder_context_set_stream_limit(ctx.handle, 0)
+        order, table = sp.csg_table(_dev(ptr), _dev(ind), ctx=ctx, **params)
+        assert np.array_equal(table.cpu().numpy().view(np.uint64), t_or)
+        ctx.close()
+
+
+def test_workspace_is_in_proportion_to_the_input():
+    # a small matrix must not make the context hold the gigabyte a large one needs
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build("rmat12")
+    ctx = sp.Context()
+    sp.chunk_similarity_greedy(_dev(ptr), _dev(ind), ctx=ctx)
+    assert ctx.workspace_bytes() < 64 << 20
+    sp.count_pillars(_dev(ptr), _dev(ind), 64, ctx=ctx)
+    assert ctx.workspace_bytes() < 64 << 20
+    ctx.close()
+
+
+def test_shard_must_hold_whole_chunks():
+    sp = _sp()
+    from chunkedgreedy_b200 import dist as csgdist
+    ptr, ind, val, sym, params = cases.build("rmat12")
+    n = ptr.size - 1
+    pl, il = csgdist.extract_shard(ptr, ind, 1000, 2024)  # starts in the middle of a chunk
+    with pytest.raises(RuntimeError, match="multiple of the chunk size"):
+        csgdist.csg_shard(_dev(pl), _dev(il), n, 1000, k=16, chunk_size=1024)
+    pl, il = csgdist.extract_shard(ptr, ind, 3072, n)
+    with pytest.raises(RuntimeError, match="does not lie inside"):
+        csgdist.csg_shard(_dev(pl), _dev(il), n - 1, 3072, k=16, chunk_size=1024)
+    order = csgdist.csg_shard(_dev(pl), _dev(il), n, 3072, k=16, chunk_size=1024)
+    assert np.array_equal(order.cpu().numpy(), oracle.csg(ptr, ind, False)[3072:])
+
+
+def test_spmm_of_a_row_block_against_the_whole_product():
+    # the row-partitioned product: a block of rows times the whole dense operand
+    sp = _sp()
+    from chunkedgreedy_b200 import dist as csgdist
+    ptr, ind, val, sym, params = cases.build("rmat16")
+    n = ptr.size - 1
+    dp, di, dv = _dev(ptr), _dev(ind), _dev(val)
+    B = torch.randn((n, 32), device="cuda")
+    whole = sp.spmm(dp, di, dv, B)
+    bounds = csgdist.spmm_row_bounds(dp, 3)
+    assert bounds[0][0] == 0 and bounds[-1][1] == n
+    for r0, r1 in bounds:
+        pl, il, vl = csgdist.spmm_shard(dp, di, dv, r0, r1)
+        part = sp.spmm(pl, il, vl, B, n_cols=n)
+        assert torch.equal(part, whole[r0:r1])
+    with pytest.raises(ValueError):
+        sp.spmm(pl, il, vl, B)  # without n_cols the operand must be square with the block
+
+
+def test_results_come_back_in_the_callers_array_framework():
+    # sporder/python/sporder/__init__.py:28-39: arrays of another framework go in through
+    # DLPack and results come back through that framework's from_dlpack
+    import sys
+    import types
+    sp = _sp()
+
+    class Foreign:
+        def __init__(self, t):
+            self.t = t
+
+        def __dlpack__(self, stream=None):
+            return self.t.__dlpack__()
+
+        def __dlpack_device__(self):
+            return self.t.__dlpack_device__()
+
+    mod = types.ModuleType("foreignxp")
+    mod.from_dlpack = lambda t: Foreign(torch.from_dlpack(t))
+    sys.modules["foreignxp"] = mod
+    Foreign.__module__ = "foreignxp.core"
+    try:
+        ptr, ind, val, sym, params = cases.build("rmat12")
+        order = sp.chunk_similarity_greedy(Foreign(_dev(ptr)), Foreign(_dev(ind)))
+        assert isinstance(order, Foreign)
+        assert np.array_equal(order.t.cpu().numpy(), oracle.csg(ptr, ind, False))
+        out = sp.reorder(Foreign(_dev(ptr)), _dev(ind), order, symmetric=True)
+        assert all(isinstance(a, Foreign) for a in out)
+        assert isinstance(sp.chunk_similarity_greedy(_dev(ptr), _dev(ind)), torch.Tensor)
+    finally:
+        del sys.modules["foreignxp"]
+
+
+def test_default_context_follows_the_arrays_device():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build("rmat12")
+    with torch.cuda.device(0):
+        dp, di = (torch.from_numpy(a).to("cuda:1") for a in (ptr, ind))
+        order = sp.chunk_similarity_greedy(dp, di)  # device 0 is current, the arrays live on 1
+        assert order.device.index == 1 and torch.cuda.current_device() == 0
+        assert np.array_equal(order.cpu().numpy(), oracle.csg(ptr, ind, False))
+
+
 def _nccl_worker(rank, world, port, result_path):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -390,8 +517,15 @@ def _nccl_worker(rank, world, port, result_path):
     from chunkedgreedy_b200 import dist as csgdist
     ptr, ind, val, sym, params = cases.build("rmat16")
     order = csgdist.chunk_similarity_greedy_sharded(ptr, ind, **params)
+    # the SpMM the reorder feeds, row-partitioned: every rank its rows, gathered for the check
+    import chunkedgreedy_b200 as sp
+    dp, di, dv = _dev(ptr), _dev(ind), _dev(val)
+    p2, i2, v2 = sp.reorder(dp, di, order, val=dv, symmetric=True)
+    B = torch.from_numpy(np.random.default_rng(9).standard_normal((ptr.size - 1, 32)).astype(np.float32)).cuda()
+    c = csgdist.spmm_sharded(p2, i2, v2, B, gather=True)
     if rank == 0:
         np.save(result_path, order.cpu().numpy())
+        np.save(result_path + ".c.npy", c.cpu().numpy())
     dist.barrier()
     dist.destroy_process_group()
 
@@ -409,4 +543,9 @@ def test_two_gpu_row_shards_equal_single_gpu(tmp_path):
     path = str(tmp_path / "order.npy")
     mp.spawn(_nccl_worker, args=(2, port, path), nprocs=2, join=True)
     ptr, ind, val, sym, params = cases.build("rmat16")
-    assert np.array_equal(np.load(path), oracle.csg(ptr, ind, False, **params))
+    want = oracle.csg(ptr, ind, False, **params)
+    assert np.array_equal(np.load(path), want)
+    rp, ri, rv = oracle.reorder(ptr, ind, want, val, symmetric=True)
+    B = np.random.default_rng(9).standard_normal((ptr.size - 1, 32)).astype(np.float32)
+    c64, cabs = oracle.spmm_f64(rp, ri, rv, B)
+    assert np.all(np.abs(np.load(path + ".c.npy") - c64) <= 1e-5 * cabs + 1e-30)
