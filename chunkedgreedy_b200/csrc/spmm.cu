@@ -7,14 +7,21 @@
 // nonzero (4*w bytes), so the kernel is a bandwidth kernel and its job is to keep
 // many row gathers in flight.
 //
-// Row tiling: a group of G = w/VEC lanes (VEC = 4 floats where w allows) owns one
-// row piece and walks its nonzeros four at a time; every lane of the group loads its
-// VEC columns of B[col] (one coalesced segment per group) and accumulates in
-// registers.  A warp therefore handles 32/G rows at once, and each group fetches its
-// next row from a ticket counter the moment it is done, so uneven row lengths do not
-// idle lanes.  Rows longer than SPLIT are cut into pieces that all groups share and
-// that are added with atomics (C is zeroed first for those rows), so a hub row never
-// serialises on one warp.
+// Row tiling: a group of G lanes owns one row and walks its nonzeros up to eight at a
+// time; every lane of the group loads its VEC columns of B[col] (one coalesced segment per
+// group), for PAN panels of G*VEC columns at once, and accumulates in registers.  A warp
+// therefore handles 32/G rows at once.  Rows are handed out in two levels.  The rows are cut
+// into units of equal cost, where a row costs ROW_COST plus its nonzeros: unit u holds the
+// rows r with ROW_COST * r + ptr[r] in [u * T, (u + 1) * T), found by searching the row
+// pointers, so a stretch of hub rows and a stretch of empty rows make equally many units.  A
+// warp draws a unit from one global counter (one atomic per unit), stages the unit's row
+// pointers in shared memory with one coalesced read, and its groups take the rows of the
+// unit one by one as they finish, so uneven row lengths idle no lanes and no counter is
+// hammered once per row.  (Batches of a fixed number of rows left the SMs idle 60 % of the
+// kernel on a power-law matrix: one warp drew 128 hub rows.)  Rows longer than SPLIT are cut
+// into pieces that all groups share and that are added with atomics (C is zeroed first for
+// those rows), so a hub row never serialises on one warp.  The matrix is read once and marked as streaming data (evict
+// first), so that it does not push rows of B out of the L2 cache.
 #include <mutex>
 
 #include "../../include/sporder_b200.h"
@@ -25,7 +32,13 @@ namespace csg {
 namespace {
 
 constexpr int M_THREADS = 256;
-constexpr int SPLIT = 1024;  // longest row piece one lane group walks
+constexpr int M_WARPS = M_THREADS / 32;
+constexpr int M_BLOCKS_PER_SM = 3;
+constexpr int SPLIT = 1024;      // longest row one lane group walks alone
+constexpr int LONG_PIECE = 256;  // nonzeros per piece of a longer row
+constexpr int ROW_COST = 4;      // cost of a row beside its nonzeros, in nonzeros
+constexpr int UNIT_MAX = 2048;   // largest unit cost; a unit holds at most UNIT_MAX / ROW_COST rows
+constexpr int BATCH_MAX = UNIT_MAX / ROW_COST;
 
 template <int VEC>
 __device__ __forceinline__ void load_b(const float *p, float (&out)[VEC]) {
@@ -45,7 +58,7 @@ __device__ __forceinline__ void load_b(const float *p, float (&out)[VEC]) {
 }
 
 struct SpmmArgs {
-  int32_t n, w;
+  int32_t n, w, nnz, unit;  // unit: cost per unit of rows (T)
   const int32_t *ptr, *ind;
   const float *val;
   const float *B;
@@ -55,36 +68,83 @@ struct SpmmArgs {
   int2 *long_rows;  // (row, first piece number), in piece order
 };
 
+// First row r in [0, n] with ROW_COST * r + ptr[r] >= target, n + 1 when there is none.  Two
+// searches at once: lanes 0-15 look for target_lo, lanes 16-31 for target_hi, sixteen probes
+// per step, so a search costs log16(n) dependent loads instead of log2(n).
+__device__ __forceinline__ void unit_bounds(const SpmmArgs &a, long long target_lo, long long target_hi,
+                                            int32_t *first, int32_t *last) {
+  const int lane = threadIdx.x & 31, i = lane & 15;
+  const long long target = lane < 16 ? target_lo : target_hi;
+  long long lo = 0, hi = static_cast<long long>(a.n) + 1;  // the answer lies in [lo, hi]
+  while (__any_sync(FULL, lo < hi)) {
+    const long long len = hi - lo;
+    const long long step = (len + 15) / 16;
+    long long idx = lo + (i + 1) * step - 1;
+    if (idx > hi - 1) idx = hi - 1;
+    bool pred = false;
+    if (lo < hi) pred = ROW_COST * idx + __ldg(a.ptr + idx) >= target;
+    const unsigned votes = (__ballot_sync(FULL, pred) >> (lane & 16)) & 0xFFFFu;
+    if (lo < hi) {
+      if (votes) {
+        const int f = __ffs(votes) - 1;
+        long long top = lo + (f + 1) * step - 1;
+        if (top > hi - 1) top = hi - 1;
+        lo = lo + f * step;
+        hi = top;
+      } else {
+        lo = hi;
+      }
+    }
+  }
+  *first = static_cast<int32_t>(__shfl_sync(FULL, lo, 0));
+  *last = static_cast<int32_t>(__shfl_sync(FULL, lo, 16));
+}
+
 constexpr int CTRL_TICKET = 0;
 constexpr int CTRL_PACKED = 2;  // 64-bit: high word = long rows queued, low word = pieces so far
 constexpr int CTRL_SCRATCH_WORDS = 64;
 
-// FMA of up to four nonzeros [p, p + cnt) of one row into acc, loads issued together.
-template <int G, int VEC>
-__device__ __forceinline__ void fma4(const SpmmArgs &a, int32_t p, int cnt, int32_t col0,
-                                     float (&acc)[VEC]) {
-  int32_t c[4];
-  float x[4];
-  float b[4][VEC];
+// gathers in flight per group and step: eight rows of B, four where a lane already
+// fetches two panels of each
+template <int PAN>
+struct Step {
+  static constexpr int U = PAN >= 2 ? 4 : 8;
+};
+
+// FMA of up to U nonzeros [p, p + cnt) of one row into acc, for the panels
+// pn0 .. pn0 + PAN - 1, all loads of a kind issued together.
+template <int G, int VEC, int PAN>
+__device__ __forceinline__ void fma_step(const SpmmArgs &a, int32_t p, int cnt, int32_t col0,
+                                         float (&acc)[PAN][VEC]) {
+  constexpr int U = Step<PAN>::U;
+  int32_t c[U];
+  float x[U];
+  float b[U][PAN][VEC];
 #pragma unroll
-  for (int u = 0; u < 4; ++u) {
+  for (int u = 0; u < U; ++u) {
     const bool on = u < cnt;
-    c[u] = on ? __ldg(a.ind + p + u) : 0;
-    x[u] = on ? __ldg(a.val + p + u) : 0.0f;
+    c[u] = on ? __ldcs(a.ind + p + u) : 0;
+    x[u] = on ? __ldcs(a.val + p + u) : 0.0f;
   }
 #pragma unroll
-  for (int u = 0; u < 4; ++u) {
+  for (int u = 0; u < U; ++u) {
     if (u < cnt) {
-      load_b<VEC>(a.B + static_cast<size_t>(c[u]) * a.w + col0, b[u]);
+      const float *src = a.B + static_cast<size_t>(c[u]) * a.w + col0;
+#pragma unroll
+      for (int pn = 0; pn < PAN; ++pn) load_b<VEC>(src + pn * G * VEC, b[u][pn]);
     } else {
 #pragma unroll
-      for (int v = 0; v < VEC; ++v) b[u][v] = 0.0f;
+      for (int pn = 0; pn < PAN; ++pn)
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) b[u][pn][v] = 0.0f;
     }
   }
 #pragma unroll
-  for (int u = 0; u < 4; ++u)
+  for (int u = 0; u < U; ++u)
 #pragma unroll
-    for (int v = 0; v < VEC; ++v) acc[v] = fmaf(x[u], b[u][v], acc[v]);
+    for (int pn = 0; pn < PAN; ++pn)
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) acc[pn][v] = fmaf(x[u], b[u][pn][v], acc[pn][v]);
 }
 
 template <int VEC>
@@ -93,106 +153,122 @@ __device__ __forceinline__ void store_c(float *out, const float (&acc)[VEC], boo
 #pragma unroll
     for (int v = 0; v < VEC; ++v) atomicAdd(out + v, acc[v]);
   } else if (VEC == 4) {
-    *reinterpret_cast<float4 *>(out) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    __stcs(reinterpret_cast<float4 *>(out), make_float4(acc[0], acc[1], acc[2], acc[3]));
   } else if (VEC == 2) {
-    *reinterpret_cast<float2 *>(out) = make_float2(acc[0], acc[1]);
+    __stcs(reinterpret_cast<float2 *>(out), make_float2(acc[0], acc[1]));
   } else {
-    out[0] = acc[0];
+    __stcs(out, acc[0]);
   }
 }
 
-// First launch.  Every lane group is persistent: it takes the next row from a ticket
-// counter as soon as its current row is finished, so the groups of a warp never wait
-// for the one with the longest row.  Rows longer than SPLIT are zeroed and queued for
-// the second launch.  (w == G * VEC here; wider matrices take the panel kernel.)
-template <int G, int VEC>
-__global__ void __launch_bounds__(M_THREADS) spmm_rows_kernel(SpmmArgs a) {
-  const int lane = threadIdx.x & 31;
+// First launch: all rows of up to SPLIT nonzeros.  Every lane group is persistent: it takes
+// the next row of its warp's unit as soon as its current row is finished, so the groups of
+// a warp never wait for the one with the longest row.  Rows longer than SPLIT are zeroed and
+// queued for the second launch.  A row is walked once per PAN panels (w = panels * G * VEC).
+template <int G, int VEC, int PAN>
+__global__ void __launch_bounds__(M_THREADS, M_BLOCKS_PER_SM) spmm_rows_kernel(SpmmArgs a) {
+  constexpr int U = Step<PAN>::U;
+  __shared__ int32_t sptr[M_WARPS][BATCH_MAX + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gl = lane % G;
-  const unsigned gmask = (G == 32) ? FULL : (((1u << G) - 1u) << (lane - gl));
-  const int32_t col0 = gl * VEC;
-  int32_t row = -1, p = 0, pe = 0;
-  bool done = false;
-  float acc[VEC];
+  const unsigned below_group = (1u << (lane - gl)) - 1u;  // lanes of the groups in front of mine
+  int32_t *wp = sptr[warp];
+  const int panels = a.w / (G * VEC);
+  // warp-uniform: the rows in hand [bfirst, bfirst + bcount) and how many of them are given out
+  int32_t bfirst = 0, bcount = 0, bnext = 0;
+  bool exhausted = false;
+  // group-uniform: the row in hand (-1: none), its extent, the walk's position and panel
+  int32_t row = -1, pb = 0, p = 0, pe = 0, pn0 = 0;
+  float acc[PAN][VEC];
 #pragma unroll
-  for (int v = 0; v < VEC; ++v) acc[v] = 0.0f;
+  for (int pn = 0; pn < PAN; ++pn)
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc[pn][v] = 0.0f;
   for (;;) {
-    if (p >= pe && !done) {
-      if (row >= 0) store_c<VEC>(a.C + static_cast<size_t>(row) * a.w + col0, acc, false);
-      int32_t r = 0;
-      if (gl == 0) r = static_cast<int32_t>(atomicAdd(&a.ctrl[CTRL_TICKET], 1u));
-      r = __shfl_sync(gmask, r, lane - gl);
-      row = -1;
-      if (r >= a.n) {
-        done = true;
-      } else {
-        const int32_t b = a.ptr[r], e = a.ptr[r + 1];
-        if (e - b > SPLIT) {
-          for (int32_t j = gl * VEC; j < a.w; j += G * VEC)
+    if (row >= 0 && p >= pe) {  // end of a walk: store, then the next panels or a new row
+      float *out = a.C + static_cast<size_t>(row) * a.w + pn0 * (G * VEC) + gl * VEC;
 #pragma unroll
-            for (int v = 0; v < VEC; ++v) a.C[static_cast<size_t>(r) * a.w + j + v] = 0.0f;
-          if (gl == 0) {
-            const unsigned long long pieces = static_cast<unsigned long long>((e - b + SPLIT - 1) / SPLIT);
-            const unsigned long long old = atomicAdd(
-                reinterpret_cast<unsigned long long *>(a.ctrl + CTRL_PACKED), (1ull << 32) | pieces);
-            a.long_rows[old >> 32] = make_int2(r, static_cast<int32_t>(old & 0xFFFFFFFFu));
-          }
+      for (int pn = 0; pn < PAN; ++pn) {
+        store_c<VEC>(out + pn * G * VEC, acc[pn], false);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) acc[pn][v] = 0.0f;
+      }
+      pn0 += PAN;
+      if (pn0 < panels)
+        p = pb;
+      else
+        row = -1;
+    }
+    const unsigned want = __ballot_sync(FULL, row < 0 && gl == 0);  // groups without a row
+    if (want) {
+      if (bnext >= bcount && !exhausted) {  // the warp draws its next unit of rows
+        uint32_t t = 0;
+        if (lane == 0) t = atomicAdd(&a.ctrl[CTRL_TICKET], 1u);
+        t = __shfl_sync(FULL, t, 0);
+        bnext = 0;
+        bcount = 0;
+        const long long total = static_cast<long long>(ROW_COST) * a.n + a.nnz;
+        if (static_cast<long long>(t) * a.unit > total) {
+          exhausted = true;
         } else {
-          row = r;
-          p = b;
-          pe = e;
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) acc[v] = 0.0f;
+          int32_t first, last;
+          unit_bounds(a, static_cast<long long>(t) * a.unit, (static_cast<long long>(t) + 1) * a.unit,
+                      &first, &last);
+          if (last > a.n) last = a.n;
+          if (first < last) {
+            bfirst = first;
+            bcount = last - first;  // at most unit / ROW_COST <= BATCH_MAX rows
+            if (bcount > BATCH_MAX) bcount = BATCH_MAX;  // (only with row pointers that decrease)
+            __syncwarp();
+            for (int k = lane; k <= bcount; k += 32) wp[k] = __ldg(a.ptr + bfirst + k);
+            __syncwarp();
+          }
         }
       }
-    }
-    if (__all_sync(FULL, done)) break;
-    const int cnt = pe - p < 4 ? pe - p : 4;
-    if (cnt > 0) fma4<G, VEC>(a, p, cnt, col0, acc);
-    p += cnt;
-  }
-}
-
-// Matrices wider than one panel of G*VEC columns: one lane group per row and panel loop.
-template <int G, int VEC>
-__global__ void __launch_bounds__(M_THREADS) spmm_panel_kernel(SpmmArgs a) {
-  constexpr int PER_WARP = 32 / G;
-  const int lane = threadIdx.x & 31;
-  const int sub = lane / G, gl = lane % G;
-  const int32_t warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int32_t warps = (gridDim.x * blockDim.x) >> 5;
-  const int panels = a.w / (G * VEC);
-  for (int32_t base = warp_global * PER_WARP; base < a.n; base += warps * PER_WARP) {
-    const int32_t row = base + sub;
-    if (row >= a.n) continue;
-    const int32_t pb = a.ptr[row], pe = a.ptr[row + 1];
-    if (pe - pb > SPLIT) {
-      for (int32_t j = gl; j < a.w; j += G) a.C[static_cast<size_t>(row) * a.w + j] = 0.0f;
-      if (gl == 0) {
-        const unsigned long long pieces = static_cast<unsigned long long>((pe - pb + SPLIT - 1) / SPLIT);
-        const unsigned long long old = atomicAdd(
-            reinterpret_cast<unsigned long long *>(a.ctrl + CTRL_PACKED), (1ull << 32) | pieces);
-        a.long_rows[old >> 32] = make_int2(row, static_cast<int32_t>(old & 0xFFFFFFFFu));
-      }
-      continue;
-    }
-    for (int panel = 0; panel < panels; ++panel) {
-      const int32_t col0 = panel * G * VEC + gl * VEC;
-      float acc[VEC];
+      if (row < 0) {
+        const int idx = bnext + __popc(want & below_group);
+        if (idx < bcount) {
+          int32_t b = wp[idx], e = wp[idx + 1];
+          if (b < 0 || e < b || e > a.nnz) e = b = 0;  // malformed row pointers: an empty row
+          const int32_t r = bfirst + idx;
+          if (e - b > SPLIT) {
+            for (int32_t j = gl * VEC; j < a.w; j += G * VEC)
 #pragma unroll
-      for (int v = 0; v < VEC; ++v) acc[v] = 0.0f;
-      for (int32_t p = pb; p < pe; p += 4) fma4<G, VEC>(a, p, pe - p < 4 ? pe - p : 4, col0, acc);
-      store_c<VEC>(a.C + static_cast<size_t>(row) * a.w + col0, acc, false);
+              for (int v = 0; v < VEC; ++v) a.C[static_cast<size_t>(r) * a.w + j + v] = 0.0f;
+            if (gl == 0) {
+              const unsigned long long pieces =
+                  static_cast<unsigned long long>((e - b + LONG_PIECE - 1) / LONG_PIECE);
+              const unsigned long long old = atomicAdd(
+                  reinterpret_cast<unsigned long long *>(a.ctrl + CTRL_PACKED), (1ull << 32) | pieces);
+              a.long_rows[old >> 32] = make_int2(r, static_cast<int32_t>(old & 0xFFFFFFFFu));
+            }
+          } else {
+            row = r;
+            pb = p = b;
+            pe = e;
+            pn0 = 0;
+          }
+        }
+      }
+      const int given = bnext + __popc(want);
+      bnext = given < bcount ? given : bcount;
+      if (exhausted && __ballot_sync(FULL, row >= 0) == 0u) break;
+    }
+    if (row >= 0 && p < pe) {
+      const int cnt = pe - p < U ? pe - p : U;
+      fma_step<G, VEC, PAN>(a, p, cnt, pn0 * (G * VEC) + gl * VEC, acc);
+      p += cnt;
     }
   }
 }
 
-// Second launch: the pieces (SPLIT nonzeros each) of the queued long rows, spread over
+// Second launch: the pieces (LONG_PIECE nonzeros each) of the queued long rows, spread over
 // all lane groups; piece number -> queue entry by binary search on the entries' first
 // piece numbers (ascending by construction).  Partial rows are added with atomics.
-template <int G, int VEC>
-__global__ void __launch_bounds__(M_THREADS) spmm_long_kernel(SpmmArgs a) {
+template <int G, int VEC, int PAN>
+__global__ void __launch_bounds__(M_THREADS, M_BLOCKS_PER_SM) spmm_long_kernel(SpmmArgs a) {
   constexpr int PER_WARP = 32 / G;
+  constexpr int U = Step<PAN>::U;
   const int lane = threadIdx.x & 31;
   const int sub = lane / G, gl = lane % G;
   const int32_t group = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * PER_WARP + sub;
@@ -211,37 +287,55 @@ __global__ void __launch_bounds__(M_THREADS) spmm_long_kernel(SpmmArgs a) {
     }
     const int2 q = a.long_rows[lo];
     const int32_t b = a.ptr[q.x], e = a.ptr[q.x + 1];
-    const int32_t pb = b + (id - q.y) * SPLIT;
-    const int32_t pe = pb + SPLIT < e ? pb + SPLIT : e;
-    for (int panel = 0; panel < panels; ++panel) {
-      const int32_t col0 = panel * G * VEC + gl * VEC;
-      float acc[VEC];
+    const int32_t pb = b + (id - q.y) * LONG_PIECE;
+    const int32_t pe = pb + LONG_PIECE < e ? pb + LONG_PIECE : e;
+    for (int pn0 = 0; pn0 < panels; pn0 += PAN) {
+      const int32_t col0 = pn0 * (G * VEC) + gl * VEC;
+      float acc[PAN][VEC];
 #pragma unroll
-      for (int v = 0; v < VEC; ++v) acc[v] = 0.0f;
-      for (int32_t p = pb; p < pe; p += 4) fma4<G, VEC>(a, p, pe - p < 4 ? pe - p : 4, col0, acc);
-      store_c<VEC>(a.C + static_cast<size_t>(q.x) * a.w + col0, acc, true);
+      for (int pn = 0; pn < PAN; ++pn)
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) acc[pn][v] = 0.0f;
+      for (int32_t p = pb; p < pe; p += U) fma_step<G, VEC, PAN>(a, p, pe - p < U ? pe - p : U, col0, acc);
+#pragma unroll
+      for (int pn = 0; pn < PAN; ++pn)
+        store_c<VEC>(a.C + static_cast<size_t>(q.x) * a.w + col0 + pn * G * VEC, acc[pn], true);
     }
   }
 }
 
-template <int G, int VEC>
-bool launch_variant(Context &ctx, const SpmmArgs &a) {
-  const int per_warp = 32 / G;
-  if (a.w == G * VEC) {  // one panel: persistent groups, a few waves worth of them
-    spmm_rows_kernel<G, VEC><<<ctx.num_sms * 8, M_THREADS, 0, ctx.stream>>>(a);
-  } else {
-    int64_t warps = (static_cast<int64_t>(a.n) + per_warp - 1) / per_warp;
-    int64_t blocks = (warps * 32 + M_THREADS - 1) / M_THREADS;
-    const int64_t cap = static_cast<int64_t>(ctx.num_sms) * 32;
-    if (blocks > cap) blocks = cap;
-    if (blocks < 1) blocks = 1;
-    spmm_panel_kernel<G, VEC><<<static_cast<int>(blocks), M_THREADS, 0, ctx.stream>>>(a);
-  }
+template <int G, int VEC, int PAN>
+bool launch_variant(Context &ctx, SpmmArgs a) {
+  // cost per unit: enough units that every warp of the grid draws several of them
+  const int grid = ctx.num_sms * M_BLOCKS_PER_SM;
+  const long long total = static_cast<long long>(ROW_COST) * a.n + a.nnz;
+  long long unit = total / (static_cast<long long>(grid) * M_WARPS * 8);
+  if (unit < 128) unit = 128;
+  if (unit > UNIT_MAX) unit = UNIT_MAX;
+  a.unit = static_cast<int32_t>(unit);
+  spmm_rows_kernel<G, VEC, PAN><<<grid, M_THREADS, 0, ctx.stream>>>(a);
   CSG_CUDA(cudaGetLastError());
-  spmm_long_kernel<G, VEC><<<ctx.num_sms * 8, M_THREADS, 0, ctx.stream>>>(a);
+  spmm_long_kernel<G, VEC, PAN><<<grid, M_THREADS, 0, ctx.stream>>>(a);
   CSG_CUDA(cudaGetLastError());
   count_launches(2);
   return true;
+}
+
+// Lane groups by dense width: float4 columns per lane where the width and the alignment of
+// B and C allow, single floats otherwise; two panels per walk when the panel count is even.
+bool dispatch_spmm(Context &ctx, const SpmmArgs &a) {
+  const int w = a.w;
+  const bool al16 = (reinterpret_cast<uintptr_t>(a.B) % 16 == 0) && (reinterpret_cast<uintptr_t>(a.C) % 16 == 0);
+  if (w % 256 == 0 && al16) return launch_variant<32, 4, 2>(ctx, a);
+  if (w % 128 == 0 && al16) return launch_variant<32, 4, 1>(ctx, a);
+  if (w % 64 == 0 && al16) return launch_variant<16, 4, 1>(ctx, a);
+  if (w % 32 == 0 && al16) return launch_variant<8, 4, 1>(ctx, a);
+  if (w % 16 == 0 && al16) return launch_variant<4, 4, 1>(ctx, a);
+  if (w % 32 == 0) return launch_variant<32, 1, 1>(ctx, a);
+  if (w % 8 == 0) return launch_variant<8, 1, 1>(ctx, a);
+  if (w % 4 == 0) return launch_variant<4, 1, 1>(ctx, a);
+  if (w % 2 == 0) return launch_variant<2, 1, 1>(ctx, a);
+  return launch_variant<1, 1, 1>(ctx, a);
 }
 
 }  // namespace
@@ -252,6 +346,8 @@ bool launch_spmm(Context &ctx, int32_t n, int32_t nnz, int32_t w, const int32_t 
   SpmmArgs a;
   a.n = n;
   a.w = w;
+  a.nnz = nnz;
+  a.unit = UNIT_MAX;
   a.ptr = d_ptr;
   a.ind = d_ind;
   a.val = d_val;
@@ -265,17 +361,7 @@ bool launch_spmm(Context &ctx, int32_t n, int32_t nnz, int32_t w, const int32_t 
   a.ctrl = reinterpret_cast<uint32_t *>(ctx.ws + o_ctrl);
   a.long_rows = reinterpret_cast<int2 *>(ctx.ws + o_rows);
   CSG_CUDA(cudaMemsetAsync(a.ctrl, 0, sizeof(uint32_t) * CTRL_SCRATCH_WORDS, ctx.stream));
-
-  const bool al16 = (reinterpret_cast<uintptr_t>(d_B) % 16 == 0) && (reinterpret_cast<uintptr_t>(d_C) % 16 == 0);
-  if (w % 128 == 0 && al16) return launch_variant<32, 4>(ctx, a);
-  if (w % 64 == 0 && al16) return launch_variant<16, 4>(ctx, a);
-  if (w % 32 == 0 && al16) return launch_variant<8, 4>(ctx, a);
-  if (w % 16 == 0 && al16) return launch_variant<4, 4>(ctx, a);
-  if (w % 32 == 0) return launch_variant<32, 1>(ctx, a);
-  if (w % 8 == 0) return launch_variant<8, 1>(ctx, a);
-  if (w % 4 == 0) return launch_variant<4, 1>(ctx, a);
-  if (w % 2 == 0) return launch_variant<2, 1>(ctx, a);
-  return launch_variant<1, 1>(ctx, a);
+  return dispatch_spmm(ctx, a);
 }
 
 }  // namespace csg
@@ -339,6 +425,8 @@ bool run_spmm_static(int32_t n, int32_t nnz, int32_t w, const int32_t *d_ptr, co
   SpmmArgs a;
   a.n = n;
   a.w = w;
+  a.nnz = nnz;
+  a.unit = UNIT_MAX;
   a.ptr = d_ptr;
   a.ind = d_ind;
   a.val = d_val;
@@ -348,17 +436,7 @@ bool run_spmm_static(int32_t n, int32_t nnz, int32_t w, const int32_t *d_ptr, co
   a.long_rows = reinterpret_cast<int2 *>(scratch + STATIC_QUEUE_OFFSET);
   // the counters keep the previous call's values: clear them (the queue is overwritten)
   CSG_CUDA(cudaMemsetAsync(a.ctrl, 0, sizeof(uint32_t) * CTRL_SCRATCH_WORDS, stream));
-  const bool al16 = (reinterpret_cast<uintptr_t>(d_B) % 16 == 0) &&
-                    (reinterpret_cast<uintptr_t>(d_C) % 16 == 0);
-  if (w % 128 == 0 && al16) return launch_variant<32, 4>(tmp, a);
-  if (w % 64 == 0 && al16) return launch_variant<16, 4>(tmp, a);
-  if (w % 32 == 0 && al16) return launch_variant<8, 4>(tmp, a);
-  if (w % 16 == 0 && al16) return launch_variant<4, 4>(tmp, a);
-  if (w % 32 == 0) return launch_variant<32, 1>(tmp, a);
-  if (w % 8 == 0) return launch_variant<8, 1>(tmp, a);
-  if (w % 4 == 0) return launch_variant<4, 1>(tmp, a);
-  if (w % 2 == 0) return launch_variant<2, 1>(tmp, a);
-  return launch_variant<1, 1>(tmp, a);
+  return dispatch_spmm(tmp, a);
 }
 
 }  // namespace

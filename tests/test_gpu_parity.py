@@ -451,12 +451,14 @@ def test_spmm_of_a_row_block_against_the_whole_product():
     dp, di, dv = _dev(ptr), _dev(ind), _dev(val)
     B = torch.randn((n, 32), device="cuda")
     whole = sp.spmm(dp, di, dv, B)
+    scale = sp.spmm(dp, di, dv.abs(), B.abs())
     bounds = csgdist.spmm_row_bounds(dp, 3)
     assert bounds[0][0] == 0 and bounds[-1][1] == n
     for r0, r1 in bounds:
         pl, il, vl = csgdist.spmm_shard(dp, di, dv, r0, r1)
         part = sp.spmm(pl, il, vl, B, n_cols=n)
-        assert torch.equal(part, whole[r0:r1])
+        # (not bitwise: the pieces of a long row are added in whatever order they finish)
+        assert torch.all((part - whole[r0:r1]).abs() <= 1e-5 * scale[r0:r1] + 1e-30)
     with pytest.raises(ValueError):
         sp.spmm(pl, il, vl, B)  # without n_cols the operand must be square with the block
 
