@@ -112,6 +112,33 @@ def test_reorder_random_permutation_long_rows():
         assert np.array_equal(gv.cpu().numpy(), rv)
 
 
+def test_reorder_hub_row_of_120k_entries_under_a_global_permutation():
+    # one row longer than any shared-memory sort can hold (the radix path, three digit
+    # passes for 140,000 columns), under a permutation that moves columns across the whole
+    # matrix, next to rows of every other size class
+    sp = _sp()
+    rng = np.random.default_rng(11)
+    n = 140_000
+    lens = rng.integers(0, 6, n)
+    lens[5] = 120_000
+    lens[77] = 4097
+    lens[78] = 4096
+    lens[79] = 33
+    rows = np.repeat(np.arange(n), lens)
+    cols = np.concatenate([rng.choice(n, l, replace=False) for l in lens])
+    from chunkedgreedy_b200.synth import coo_to_csr
+    ptr, ind, val = coo_to_csr(n, rows, cols, rng.standard_normal(rows.size))
+    order = rng.permutation(n).astype(np.int32)
+    for symmetric in (True, False):
+        rp, ri, rv = oracle.reorder(ptr, ind, order, val, symmetric=symmetric)
+        gp, gi, gv = sp.reorder(_dev(ptr), _dev(ind), _dev(order), val=_dev(val), symmetric=symmetric)
+        assert np.array_equal(gp.cpu().numpy(), rp)
+        assert np.array_equal(gi.cpu().numpy(), ri)
+        assert np.array_equal(gv.cpu().numpy(), rv)
+        gp2, gi2 = sp.reorder(_dev(ptr), _dev(ind), _dev(order), symmetric=symmetric)
+        assert np.array_equal(gi2.cpu().numpy(), ri)
+
+
 def test_reorder_round_trip_is_identity():
     sp = _sp()
     ptr, ind, val, sym, params = cases.build("rmat12")
