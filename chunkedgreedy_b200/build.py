@@ -37,8 +37,10 @@ def needs_build():
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 
 
-def build(force=False, verbose=False):
-    if not force and not needs_build():
+def build(force=False, verbose=False, profile_rounds=False):
+    """``profile_rounds``: compile the chain kernel of the sketch stage with cycle counters per
+    phase of a round (-DCSG_ROUND_PROFILE; a diagnostic build, slower, never the default)."""
+    if not force and not profile_rounds and not needs_build():
         return LIB
     objs = []
     procs = []
@@ -46,6 +48,7 @@ def build(force=False, verbose=False):
     for src in SOURCES:
         obj = os.path.join(HERE, "build", src.replace(".cu", ".o"))
         cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
+              (["-DCSG_ROUND_PROFILE=%d" % int(profile_rounds)] if profile_rounds else []) + \
               ["-c", os.path.join(CSRC, src), "-o", obj]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
                                             text=True)))
@@ -63,4 +66,5 @@ def build(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv,
+                profile_rounds=2 if "--profile-rounds=2" in sys.argv else int("--profile-rounds" in sys.argv)))

@@ -4,6 +4,7 @@
 
 #include <atomic>
 #include <chrono>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -189,6 +190,37 @@ bool finish_call(Context &ctx, const CsgScratch &s) {
   uint64_t need = (static_cast<uint64_t>(h[CTRL_HEAVY_NEED + 1]) << 32) | h[CTRL_HEAVY_NEED];
   if (need > STREAM_CAP_MAX) need = STREAM_CAP_MAX;
   if (need > ctx.stream_need_seen) ctx.stream_need_seen = need;
+#ifdef CSG_ROUND_PROFILE
+  if (getenv("CSG_ROUND_PROFILE")) {  // cycles per phase of the chain kernel's rounds, all warps
+    unsigned long long c[12];
+    if (cudaMemcpy(c, s.ctrl + CTRL_PROFILE, sizeof(c), cudaMemcpyDeviceToHost) == cudaSuccess && c[6])
+      fprintf(stderr,
+              "[rounds] %llu rounds, %.2f elements each; cycles per round: look-up %.0f, order %.0f, "
+              "resolve %.0f, targets %.0f, limits %.0f, apply %.0f\n",
+              c[6], double(c[7]) / c[6], double(c[0]) / c[6], double(c[1]) / c[6], double(c[2]) / c[6],
+              double(c[3]) / c[6], double(c[4]) / c[6], double(c[5]) / c[6]);
+    uint32_t heavy = 0;
+    cudaMemcpy(&heavy, s.ctrl + CTRL_HEAVY_ROWS, sizeof(heavy), cudaMemcpyDeviceToHost);
+    if (heavy > 4096) heavy = 4096;
+    static uint32_t kcyc[4096], work[4096];
+    static int32_t rows[4096];
+    if (heavy && cudaMemcpy(kcyc, s.heavy_off, heavy * 4, cudaMemcpyDeviceToHost) == cudaSuccess &&
+        cudaMemcpy(rows, s.row_list, heavy * 4, cudaMemcpyDeviceToHost) == cudaSuccess) {
+      for (uint32_t i = 0; i < heavy; ++i)
+        cudaMemcpy(&work[i], s.row_work + rows[i], 4, cudaMemcpyDeviceToHost);
+      fprintf(stderr, "[rounds] %u heavy rows; slowest (row: stream elements, Mcycles, cycles/element):", heavy);
+      for (int k = 0; k < 12; ++k) {
+        uint32_t best = 0;
+        for (uint32_t i = 1; i < heavy; ++i)
+          if (kcyc[i] > kcyc[best]) best = i;
+        fprintf(stderr, " [%d: %u, %.1f, %.0f]", rows[best], work[best], kcyc[best] * 1024e-6,
+                work[best] ? kcyc[best] * 1024.0 / work[best] : 0.0);
+        kcyc[best] = 0;
+      }
+      fprintf(stderr, "\n");
+    }
+  }
+#endif
   return true;
 }
 

@@ -122,7 +122,8 @@ enum {
   CTRL_BUCKET_BASE = 56,   // 33 entries
   CTRL_BUCKET_FILL = 96,   // 33 entries
   CTRL_STATS = 136,        // see greedy.cu (8-byte aligned)
-  CTRL_WORDS = 168
+  CTRL_PROFILE = 168,      // 16 64-bit counters, written only by a build with -DCSG_ROUND_PROFILE
+  CTRL_WORDS = 200
 };
 
 constexpr int SKETCH_PART_COLS = 128;   // columns of a heavy row whose stream one warp writes out

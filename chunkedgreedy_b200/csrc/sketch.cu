@@ -218,6 +218,56 @@ struct Sketch {
     }
   }
 
+  // ---- steps with a key -> slot table --------------------------------------------------
+  // One byte per row of the chunk in shared memory (0 = not in the sketch, else slot + 1)
+  // answers "is the key there, and where" with one broadcast load instead of CELLS compares
+  // and a warp reduction, and the victim is only looked for when an element misses (two
+  // reductions per miss, none per hit).  Fewer instructions per element than add_full, which
+  // is what counts where many warps share a scheduler; add_full's speculation buys latency,
+  // which counts where a warp has a scheduler to itself.
+  __device__ __forceinline__ void add_filling_tab(int32_t s, float a, uint8_t *tab, int32_t cbase) {
+    const int q = tab[s - cbase];
+    if (q) {  // (same address in all lanes: the branch is uniform)
+      add_weight(q - 1, a);
+      return;
+    }
+    put(filled, s, a);
+    if (lane == 0) tab[s - cbase] = static_cast<uint8_t>(filled + 1);
+    ++filled;
+    if (filled == 32 * CELLS) lane_top2();
+    __syncwarp();
+  }
+
+  __device__ __forceinline__ void add_full_tab(int32_t s, float a, uint8_t *tab, int32_t cbase) {
+    const int q = tab[s - cbase];
+    if (q) {  // hit
+      add_weight(q - 1, a);
+      lane_top2();
+      return;
+    }
+    find_victim(l1w, l1c, gmin, gown, gcell);
+    const float wnew = __uint_as_float(gmin) + a;
+    const int32_t gslot = gown * CELLS + gcell;
+    if (lane == gown) {
+      int32_t old_key = key[0];
+#pragma unroll
+      for (int c = 1; c < CELLS; ++c) old_key = (c == gcell) ? key[c] : old_key;
+      tab[old_key - cbase] = 0;
+      tab[s - cbase] = static_cast<uint8_t>(gslot + 1);
+    }
+    put(gslot, s, wnew);
+    lane_top2();
+    __syncwarp();
+  }
+
+  // the table is empty again for the next row
+  __device__ __forceinline__ void clear_tab(uint8_t *tab, int32_t cbase) const {
+#pragma unroll
+    for (int c = 0; c < CELLS; ++c)
+      if (key[c] >= 0) tab[key[c] - cbase] = 0;
+    __syncwarp();
+  }
+
   __device__ __forceinline__ void local_sort_descending() {
     // the reference's selection sort, including where it stops
 #pragma unroll
@@ -456,6 +506,16 @@ __device__ __forceinline__ void consume(Sketch<CELLS> &sk, const int32_t *bs, co
   }
 }
 
+// The same with the key -> slot table (see Sketch::add_full_tab).
+template <int CELLS>
+__device__ __forceinline__ void consume_tab(Sketch<CELLS> &sk, uint8_t *tab, int32_t cbase, const int32_t *bs,
+                                            const float *ba, int cnt) {
+  int t = 0;
+  for (; t < cnt && sk.filled < 32 * CELLS; ++t) sk.add_filling_tab(bs[t], ba[t], tab, cbase);
+#pragma unroll 1
+  for (; t < cnt; ++t) sk.add_full_tab(bs[t], ba[t], tab, cbase);
+}
+
 __device__ __forceinline__ bool row_bounds_ok(const SketchArgs &a, int32_t rb, int32_t re) {
   if (rb < 0 || re < rb || re > a.nnz) {  // malformed row pointers: flag and skip
     if (lane_id() == 0) atomicExch(&a.ctrl[CTRL_BAD_INPUT], 1u);
@@ -465,14 +525,23 @@ __device__ __forceinline__ bool row_bounds_ok(const SketchArgs &a, int32_t rb, i
 }
 
 // All rows below the heavy threshold: one warp per row, producing and consuming in turn.
-template <int CELLS>
-__global__ void __launch_bounds__(S_THREADS) sketch_kernel(SketchArgs a, int after_primary) {
+// TAB: with a key -> slot table per warp (tab_bytes each, dynamic shared memory); without it
+// for chunks whose tables would not fit and for sketches of more than 224 slots (the table
+// holds slot numbers in a byte).
+template <int CELLS, bool TAB>
+__global__ void __launch_bounds__(S_THREADS) sketch_kernel(SketchArgs a, int after_primary, int tab_bytes) {
+  extern __shared__ __align__(16) unsigned char light_dyn[];
   __shared__ int32_t ring_s[S_WARPS][S_RING];
   __shared__ float ring_a[S_WARPS][S_RING];
   const int lane = lane_id(), warp = threadIdx.x >> 5;
   const uint32_t listed = a.ctrl[CTRL_ROWS_LISTED];
   int32_t *bs = ring_s[warp];
   float *ba = ring_a[warp];
+  uint8_t *tab = light_dyn + static_cast<size_t>(warp) * tab_bytes;
+  if (TAB) {
+    for (int i = lane * 16; i < tab_bytes; i += 32 * 16) *reinterpret_cast<uint4 *>(tab + i) = make_uint4(0, 0, 0, 0);
+    __syncwarp();
+  }
   Sketch<CELLS> sk;
   sk.bind_lane();
   Producer<S_RING> prod(a);
@@ -484,14 +553,19 @@ __global__ void __launch_bounds__(S_THREADS) sketch_kernel(SketchArgs a, int aft
     const int32_t r = a.row_list[item];
     const int32_t rb = a.ptr[r], re = a.ptr[r + 1];
     if (!row_bounds_ok(a, rb, re)) continue;
+    const int32_t cbase = (r / a.chunk) * a.chunk;
     sk.clear();
     prod.begin(r, rb, re, re - rb);
     for (;;) {
       const int cnt = prod.produce(bs, ba);
       if (cnt == 0) break;
-      consume<CELLS>(sk, bs, ba, cnt);
+      if (TAB)
+        consume_tab<CELLS>(sk, tab, cbase, bs, ba, cnt);
+      else
+        consume<CELLS>(sk, bs, ba, cnt);
       __syncwarp();
     }
+    if (TAB) sk.clear_tab(tab, cbase);
     sk.select_top_k(a.k, a.table + static_cast<size_t>(r) * a.k, a.row_base);
   }
   // Launched as the programmatic dependent of the heavy-chain kernel, this kernel starts
@@ -749,8 +823,30 @@ __global__ void __launch_bounds__(S_THREADS, 1) heavy_consume_kernel(SketchArgs 
 // On the longest R-MAT rows a round resolves 16 elements on average in about 1000 cycles,
 // where 16 sequential steps take 2200.  State lives in shared memory: weights and keys by
 // slot code, a key -> slot table over the chunk's rows, and the per-round order.
+// Diagnostic builds (python -m chunkedgreedy_b200.build --profile-rounds[=2]), printed by the
+// host when CSG_ROUND_PROFILE is set in the environment: -DCSG_ROUND_PROFILE=1 records the
+// run time of every heavy row (two clock reads per row), =2 also the cycles per phase of the
+// longest row's whole-window rounds (which slows those rounds down).
+#if defined(CSG_ROUND_PROFILE) && CSG_ROUND_PROFILE >= 2
+#define PROF_DECL unsigned long long prof_t0 = clock64(), prof_t1
+#define PROF_MARK(i)                                \
+  do {                                              \
+    prof_t1 = clock64();                            \
+    prof[i] += prof_t1 - prof_t0;                   \
+    prof_t0 = prof_t1;                              \
+  } while (0)
+#define PROF_ADD(i, v) prof[i] += (v)
+#else
+#define PROF_DECL
+#define PROF_MARK(i)
+#define PROF_ADD(i, v)
+#endif
+
 constexpr int H_RING = 1024;    // stream elements staged per batch
 constexpr int ROUND_CELLS = 4;  // largest sketch (cells per lane) resolved in rounds
+constexpr int WINDOW_PAYS = 18;    // elements whole-window rounds must resolve on average to beat strict rounds
+constexpr int WINDOW_RETRY = 24;   // the mean a row starts from when it tries the window again
+constexpr int STRICT_ROUNDS = 48;  // strict rounds in between
 constexpr int ROUND_RING_BYTES = S_WARPS * 2 * H_RING * 8;
 
 template <int CELLS>
@@ -909,6 +1005,194 @@ __device__ __forceinline__ int round_full(RoundState<CELLS> &st, uint8_t *tab, i
   return L;
 }
 
+// One round on a full sketch of 64 slots or more that resolves the WHOLE window.  The three
+// conditions of round_full end a prefix at the first element whose outcome cannot be read off
+// the order of S0 directly.  Almost all of those are hits on an entry that the misses of the
+// window are about to take, and their outcome still follows from S0 by a little bookkeeping:
+//   * the misses take the entries of S0 in order, but skip an entry that a hit has made
+//     heavier before they reached it (put back one Dice term heavier, an entry lands behind
+//     everything a window of 32 can take: checked below, not assumed);
+//   * an element whose key S0 holds in an entry that was taken before the element's turn is
+//     a miss, not a hit, and takes the next entry like any other miss;
+//   * a second element with the key of an earlier one is a hit on the entry the first one
+//     left, whichever kind the first one was.
+// Only the first element of each key ("leader") with its entry among the 32 lightest can go
+// either way.  Those are walked in stream order (a handful per window, state in two 32-bit
+// masks, every lane computing the same): with P misses before element j and b skipped entries
+// below its entry's rank r, the entry is gone iff P + b > r.  The miss with i misses before it
+// then takes the (i+1)-th entry that no hit holds back.  The read-off is exact as long as
+// nothing put back or made heavier is light enough to be taken again inside the window; an
+// element whose new weight does not clear the heaviest entry taken ends the prefix before the
+// next miss behind it (before itself, if its weight did not grow at all).  On the heaviest
+// R-MAT rows that happens in one window of 32,000 (the row's own Dice terms dominate) to one
+// in ten (rows whose terms vary more), and a round resolves 32.0 resp. 29.3 elements where
+// round_full resolves 16.
+#ifdef CSG_WINDOW_FENCES
+#define WINDOW_FENCE(s) phase_fence(s)
+#else
+#define WINDOW_FENCE(s)
+#endif
+template <int CELLS, bool TAB>
+__device__ __forceinline__ int round_window(RoundState<CELLS> &st, uint8_t *tab, uint32_t *mates,
+                                            int32_t cbase, const int2 *ring, int p, int cnt, int lane,
+                                            uint32_t &sink, unsigned long long *prof) {
+  constexpr int M = 32 * CELLS;
+  static_assert(CELLS >= 2, "a window of 32 needs more than 32 slots");
+  const uint32_t below = (1u << lane) - 1u;
+  PROF_DECL;
+  WINDOW_FENCE(sink);
+  const bool valid = p + lane < cnt;
+  const int2 elem = valid ? ring[p + lane] : make_int2(0, 0);
+  const int32_t s = elem.x;
+  const float al = __int_as_float(elem.y);
+  // Lanes that carry the same key: every lane sets its bit in a word of shared memory under
+  // its key and reads the word back (cleared again at the end of the round).  match.any, the
+  // instruction made for this, takes some 380 cycles here; it serves chunks too large for
+  // the table.
+  if (mates != nullptr && valid) atomicOr(&mates[s - cbase], 1u << lane);
+  uint32_t mine[CELLS];
+  int32_t mykey[CELLS];
+#pragma unroll
+  for (int c = 0; c < CELLS; ++c) {
+    mine[c] = st.w[c * 32 + lane];
+    mykey[c] = st.key[c * 32 + lane];
+  }
+  const int q = valid ? slot_of<CELLS, TAB>(st, tab, cbase, s) : -1;
+  const bool present = valid && q >= 0;  // S0 holds the key
+  const uint32_t wq = st.w[present ? q : 0];
+  WINDOW_FENCE(sink);
+  PROF_MARK(0);
+  // position of this lane's slots in the (weight, code) order of S0 (see round_full)
+  int pos[CELLS];
+  {
+    int32_t acc[CELLS][4];
+#pragma unroll
+    for (int c = 0; c < CELLS; ++c) acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0;
+    uint4 v[M / 4];
+#pragma unroll
+    for (int i4 = 0; i4 < M / 4; ++i4) v[i4] = reinterpret_cast<const uint4 *>(st.w)[i4];
+#pragma unroll
+    for (int i4 = 0; i4 < M / 4; ++i4) {
+      const uint32_t x[4] = {v[i4].x, v[i4].y, v[i4].z, v[i4].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = i4 * 4 + e, ci = i >> 5, li = i & 31;
+        const uint32_t lower = (below >> li) & 1u;
+#pragma unroll
+        for (int c = 0; c < CELLS; ++c) {
+          uint32_t d = x[e] - mine[c];
+          if (ci < c) d -= 1u;
+          else if (ci == c) d -= lower;
+          acc[c][e] += static_cast<int32_t>(d) >> 31;
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < CELLS; ++c) pos[c] = -((acc[c][0] + acc[c][1]) + (acc[c][2] + acc[c][3]));
+  }
+#pragma unroll
+  for (int c = 0; c < CELLS; ++c) st.rank[c * 32 + lane] = pos[c];
+  __syncwarp();
+  WINDOW_FENCE(sink);
+  PROF_MARK(1);
+  const int rho = present ? st.rank[q] : M;
+  unsigned same;
+  if (mates != nullptr)
+    same = valid ? mates[s - cbase] : 0u;
+  else
+    same = __match_any_sync(FULL, valid ? s : -1 - lane);
+  const bool leader = valid && (same & below) == 0u;  // first element of its key in the window
+  // Which leaders miss: those S0 does not hold, and those whose entry is gone by their turn.
+  // An open element (leader, entry among the 32 lightest) with `before` certain misses and
+  // `nth` open elements in front of it: at least `before`, at most `before + nth` entries
+  // below its own are taken or skipped by its turn, so rank < before means gone and
+  // rank >= before + nth means still there, whatever the open elements in front did.  Most
+  // windows have only such elements; the others are walked in stream order.
+  const uint32_t absent = __ballot_sync(FULL, leader && !present);
+  const bool open = leader && present && rho < 32;
+  uint32_t open_set = __ballot_sync(FULL, open);
+  const int slack = rho - __popc(absent & below);
+  const bool sure_gone = open && slack < 0;
+  const bool sure_held = open && slack >= __popc(open_set & below);
+  uint32_t flipped = __ballot_sync(FULL, sure_gone);  // lanes whose entry was taken before their turn
+  uint32_t held = __reduce_or_sync(FULL, sure_held ? 1u << (rho & 31) : 0u);  // ranks a hit holds back
+  if (__any_sync(FULL, open && !sure_gone && !sure_held)) {
+    flipped = 0u;
+    held = 0u;
+    while (open_set) {
+      const int j = __ffs(open_set) - 1;
+      open_set &= open_set - 1u;
+      const int r = __shfl_sync(FULL, rho, j);
+      const int before = __popc((absent | flipped) & ((1u << j) - 1u));
+      const int skipped = __popc(held & ((1u << r) - 1u));
+      if (before + skipped > r)
+        flipped |= 1u << j;
+      else
+        held |= 1u << r;
+    }
+  }
+  PROF_MARK(2);
+  const uint32_t missing = absent | flipped;
+  const int mtot = __popc(missing);
+  const bool miss = (missing >> lane) & 1u;
+  // The i-th miss takes the i-th entry of the order that no hit holds back: the owners of those
+  // entries write them out in that numbering (rank minus the held ranks below it).
+#pragma unroll
+  for (int c = 0; c < CELLS; ++c) {
+    const int r = pos[c];
+    if (r < 32 && ((held >> r) & 1u) == 0u) {
+      const int at = r - __popc(held & ((1u << r) - 1u));
+      st.sw[at] = mine[c];
+      st.si[at] = c * 32 + lane;
+      st.sk[at] = mykey[c];
+      st.miss_pos[at] = r;
+    }
+  }
+  __syncwarp();
+  WINDOW_FENCE(sink);
+  PROF_MARK(3);
+  const int mine_i = miss ? __popc(missing & below) : 0;
+  const int last_i = mtot > 0 ? mtot - 1 : 0;
+  const int tgt = st.si[mine_i];
+  const uint32_t base = st.sw[mine_i];
+  const int32_t old_key = st.sk[mine_i];
+  const uint32_t top = st.sw[last_i];
+  const int t_last = mtot > 0 ? st.miss_pos[last_i] : -1;  // rank of the heaviest entry taken
+  const uint32_t behind = missing & ~(below | (1u << lane));
+  const int next_miss = behind ? __ffs(behind) - 1 : 32;
+  const uint32_t nb = __float_as_uint(__uint_as_float(base) + al);
+  const uint32_t hv = __float_as_uint(__uint_as_float(wq) + al);
+  int lim = valid ? 32 : lane;
+  if (mtot > 0) {
+    if (miss && nb <= top) lim = nb > base ? next_miss : lane;
+    if (leader && present && !miss && rho <= t_last && hv <= top) lim = hv > wq ? next_miss : lane;
+  }
+  WINDOW_FENCE(sink);
+  int L = static_cast<int>(__reduce_min_sync(FULL, static_cast<uint32_t>(lim)));
+  L = L < 1 ? 1 : L;  // one element alone is always resolved exactly
+  PROF_MARK(4);
+  const bool applies = lane < L && leader;
+  const int times = __popc(same & (L >= 32 ? FULL : (1u << L) - 1u));
+  float wv = miss ? __uint_as_float(nb) : __uint_as_float(hv);
+  for (int k = 1; k < times; ++k) wv += al;  // later elements of the key, in stream order
+  if (TAB && applies && miss) tab[old_key - cbase] = 0;
+  if (mates != nullptr && valid) mates[s - cbase] = 0u;
+  // (a key taken by one miss may be put back by a later one, which then is a flipped lane:
+  // clear first, then set)
+  if (flipped) __syncwarp();
+  if (applies && miss) {
+    st.key[tgt] = s;
+    st.w[tgt] = __float_as_uint(wv);
+    if (TAB) tab[s - cbase] = static_cast<uint8_t>(tgt + 1);
+  }
+  if (applies && !miss) st.w[q] = __float_as_uint(wv);
+  __syncwarp();
+  PROF_MARK(5);
+  PROF_ADD(6, 1);
+  PROF_ADD(7, L);
+  return L;
+}
+
 // One round while the sketch has empty slots; `filled` is updated.
 template <int CELLS, bool TAB>
 __device__ __forceinline__ int round_fill(RoundState<CELLS> &st, uint8_t *tab, int32_t cbase,
@@ -960,21 +1244,69 @@ __device__ __forceinline__ void stage_batch(int2 *ring, const int2 *in, int cnt,
   asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
+// The two kinds of round on a full sketch as functions of their own (like rounds_row below:
+// compiled into one body, each kind loses a third of its speed to the other's registers and
+// schedule).  Strict rounds on [p, cnt) of a batch, at most `left` of them.
+template <int CELLS, bool TAB>
+__device__ __noinline__ int strict_rounds(RoundState<CELLS> &st, uint8_t *tab, int32_t cbase,
+                                          const int2 *ring, int p, int cnt, int &left) {
+  const int lane = lane_id();
+  uint32_t sink = 0;
+  while (p < cnt && left > 0) {
+    p += round_full<CELLS, TAB>(st, tab, cbase, ring, p, cnt, lane, sink);
+    --left;
+  }
+  if (lane == 0) st.fence_sink = sink;
+  return p;
+}
+
+// Whole-window rounds on [p, cnt) of a batch until the running mean of what they resolve
+// (mean4: four times the mean) falls below WINDOW_PAYS; then `left` strict rounds are due.
+template <int CELLS, bool TAB>
+__device__ __noinline__ int window_rounds(RoundState<CELLS> &st, uint8_t *tab, uint32_t *mates,
+                                          int32_t cbase, const int2 *ring, int p, int cnt, int &mean4,
+                                          int &left, unsigned long long *prof) {
+  const int lane = lane_id();
+  uint32_t sink = 0;
+  while (p < cnt) {
+    const int got = round_window<CELLS, TAB>(st, tab, mates, cbase, ring, p, cnt, lane, sink, prof);
+    const bool whole = p + got < cnt;  // (a window cut short by the end of a batch says nothing)
+    p += got;
+    if (whole) {
+      mean4 = mean4 - (mean4 >> 2) + got;
+      if (mean4 < 4 * WINDOW_PAYS) {
+        left = STRICT_ROUNDS;
+        mean4 = 4 * WINDOW_RETRY;
+        break;
+      }
+    }
+  }
+  if (lane == 0) st.fence_sink = sink;
+  return p;
+}
+
 // One heavy row, start to finish: stream batches in, rounds, final sketch out.  Not
 // inlined: compiled as part of the kernel's ticket loop the same rounds take 1280 cycles
 // instead of 1000.
 template <int CELLS, bool TAB>
 __device__ __noinline__ void rounds_row(const int2 *in, uint32_t total, int32_t cbase,
-                                        RoundState<CELLS> &st, uint8_t *tab, int2 *ring0, int2 *ring1,
-                                        int32_t *out) {
+                                        RoundState<CELLS> &st, uint8_t *tab, uint32_t *mates, int2 *ring0,
+                                        int2 *ring1, int32_t *out, unsigned long long *prof_out) {
   constexpr int M = 32 * CELLS;
   const int lane = lane_id();
+  unsigned long long prof[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+  (void)prof;
+  (void)prof_out;
 #pragma unroll
   for (int c = 0; c < CELLS; ++c) {
     st.key[c * 32 + lane] = -1;
     st.w[c * 32 + lane] = 0u;
   }
-  int filled = 0, buf = 0;
+#ifdef CSG_STRICT_ONLY
+  int filled = 0, buf = 0, strict_left = 1 << 30, mean4 = 4 * 32;
+#else
+  int filled = 0, buf = 0, strict_left = 0, mean4 = 4 * 32;
+#endif
   uint32_t sink = 0;
   __syncwarp();
   stage_batch(ring0, in, static_cast<int>(total < H_RING ? total : H_RING), lane);
@@ -990,7 +1322,33 @@ __device__ __noinline__ void rounds_row(const int2 *in, uint32_t total, int32_t 
     const int2 *ring = buf ? ring1 : ring0;
     int p = 0;
     while (p < cnt && filled < M) p += round_fill<CELLS, TAB>(st, tab, cbase, ring, p, cnt, lane, filled);
-    while (p < cnt) p += round_full<CELLS, TAB>(st, tab, cbase, ring, p, cnt, lane, sink);
+    if constexpr (CELLS >= 2) {
+      // A whole-window round costs half as much again as a strict one and pays where it
+      // resolves (nearly) the whole window: rows whose own length dominates their Dice terms.
+      // Where the terms vary widely, entries put back light are taken again at once, either
+      // kind of round ends after a few elements and the cheaper one wins.  The row decides by
+      // a running mean of what its whole-window rounds resolve: below WINDOW_PAYS the next
+      // STRICT_ROUNDS rounds are strict ones, then the window is tried again.
+      while (p < cnt) {
+        if (strict_left > 0) {
+          p = strict_rounds<CELLS, TAB>(st, tab, cbase, ring, p, cnt, strict_left);
+          continue;
+        }
+        const int got = round_window<CELLS, TAB>(st, tab, mates, cbase, ring, p, cnt, lane, sink, prof);
+        const bool whole = p + got < cnt;  // (a window cut short by the end of a batch says nothing)
+        p += got;
+        if (whole) {
+          mean4 = mean4 - (mean4 >> 2) + got;
+          if (mean4 < 4 * WINDOW_PAYS) {
+            strict_left = STRICT_ROUNDS;
+            mean4 = 4 * WINDOW_RETRY;
+          }
+        }
+      }
+    } else {  // 32 slots: a window of 32 can take every entry, the strict prefix rule stays
+      int all = 1 << 30;
+      p = strict_rounds<CELLS, TAB>(st, tab, cbase, ring, p, cnt, all);
+    }
     buf ^= 1;
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -1002,11 +1360,15 @@ __device__ __noinline__ void rounds_row(const int2 *in, uint32_t total, int32_t 
     if (TAB && kk >= 0) tab[kk - cbase] = 0;  // the table is empty again for the next row
   }
   if (lane == 0) st.fence_sink = sink;
+#ifdef CSG_ROUND_PROFILE
+  if (lane == 0 && prof_out != nullptr)
+    for (int i = 0; i < 12; ++i) atomicAdd(prof_out + i, prof[i]);
+#endif
   __syncwarp();
 }
 
 template <int CELLS>
-__global__ void __launch_bounds__(S_THREADS, 1) heavy_rounds_kernel(SketchArgs a, int tab_bytes) {
+__global__ void __launch_bounds__(S_THREADS, 1) heavy_rounds_kernel(SketchArgs a, int tab_bytes, int mates_words) {
   // dynamic shared memory: two stream buffers per warp (the next batch lands while this
   // one is consumed), then the key tables
   extern __shared__ __align__(16) unsigned char heavy_dyn[];
@@ -1016,6 +1378,13 @@ __global__ void __launch_bounds__(S_THREADS, 1) heavy_rounds_kernel(SketchArgs a
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t heavy = a.ctrl[CTRL_HEAVY_ROWS];
   uint8_t *tab = heavy_dyn + ROUND_RING_BYTES + static_cast<size_t>(warp) * tab_bytes;
+  // (behind the four key tables: a word per row of the chunk and warp for round_window's
+  // duplicate detection, when it fits)
+  uint32_t *mates = mates_words > 0
+                        ? reinterpret_cast<uint32_t *>(heavy_dyn + ROUND_RING_BYTES + static_cast<size_t>(S_WARPS) * tab_bytes) +
+                              static_cast<size_t>(warp) * mates_words
+                        : nullptr;
+  for (int i = lane; i < mates_words; i += 32) mates[i] = 0u;
   for (int i = lane * 16; i < tab_bytes; i += 32 * 16) *reinterpret_cast<uint4 *>(tab + i) = make_uint4(0, 0, 0, 0);
   for (;;) {
     uint32_t item = 0;
@@ -1024,12 +1393,25 @@ __global__ void __launch_bounds__(S_THREADS, 1) heavy_rounds_kernel(SketchArgs a
     if (item >= heavy) break;
     const int32_t r = a.row_list[item];
     int32_t *out = a.heavy_state + static_cast<size_t>(item) * (2 * CELLS * 32);
+#ifdef CSG_ROUND_PROFILE
+    const unsigned long long row_t0 = clock64();
+    const uint32_t row_off = a.heavy_off[item];
+#endif
     if (tab_bytes > 0)
       rounds_row<CELLS, true>(a.hstream + a.heavy_off[item], a.row_work[r], (r / a.chunk) * a.chunk,
-                              state[warp], tab, rings[warp][0], rings[warp][1], out);
+                              state[warp], tab, mates, rings[warp][0], rings[warp][1], out,
+                              item == 0 ? reinterpret_cast<unsigned long long *>(a.ctrl + CTRL_PROFILE)
+                                        : nullptr);  // (profile build: the longest row only)
     else  // chunk too large for key tables in shared memory
       rounds_row<CELLS, false>(a.hstream + a.heavy_off[item], a.row_work[r], 0, state[warp], nullptr,
-                               rings[warp][0], rings[warp][1], out);
+                               nullptr, rings[warp][0], rings[warp][1], out,
+                               reinterpret_cast<unsigned long long *>(a.ctrl + CTRL_PROFILE));
+#ifdef CSG_ROUND_PROFILE
+    // the row's stream offset is no longer needed: its place takes the row's run time (in
+    // units of 1024 cycles), for the host to list the slowest rows
+    (void)row_off;
+    if (lane == 0) a.heavy_off[item] = static_cast<uint32_t>((clock64() - row_t0) >> 10);
+#endif
   }
 }
 
@@ -1073,10 +1455,14 @@ bool launch_cells(Context &ctx, const SketchArgs &a) {
     const int pad = ctx.smem_optin - 1024 - static_cast<int>(fa.sharedSizeBytes);
     int64_t tab_bytes = (static_cast<int64_t>(a.chunk) + 15) / 16 * 16;
     if (ROUND_RING_BYTES + tab_bytes * S_WARPS > pad) tab_bytes = 0;  // slots found by comparing keys
+    // round_window's duplicate detector: four bytes per row of the chunk and warp, if they fit too
+    int64_t mates_words = tab_bytes;
+    if (tab_bytes == 0 || ROUND_RING_BYTES + 5 * tab_bytes * S_WARPS > pad) mates_words = 0;
     {
       CSG_CUDA(cudaFuncSetAttribute(heavy_rounds_kernel<CELLS>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, pad));
-      heavy_rounds_kernel<CELLS><<<ctx.num_sms, S_THREADS, pad, ctx.stream>>>(a, static_cast<int>(tab_bytes));
+      heavy_rounds_kernel<CELLS><<<ctx.num_sms, S_THREADS, pad, ctx.stream>>>(a, static_cast<int>(tab_bytes),
+                                                                            static_cast<int>(mates_words));
       CSG_CUDA(cudaGetLastError());
       in_rounds = true;
     }
@@ -1092,20 +1478,40 @@ bool launch_cells(Context &ctx, const SketchArgs &a) {
   // as a programmatic dependent launch, so its blocks are placed only after every block
   // of the chain kernel is running (and has its SM to itself), and it fills the SMs that
   // stay or fall free.  It waits for the chain kernel before it ends (see sketch_kernel).
-  int per_sm = 0;
-  CSG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sketch_kernel<CELLS>, S_THREADS, 0));
-  if (per_sm < 1) per_sm = 1;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(ctx.num_sms * per_sm);
-  cfg.blockDim = dim3(S_THREADS);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = ctx.stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  CSG_CUDA(cudaLaunchKernelEx(&cfg, sketch_kernel<CELLS>, a, 1));
+  // key -> slot tables for its warps when a chunk's table is small enough that the blocks of an
+  // SM still fit (16 KB per block) and slot numbers fit a byte
+  int light_tab = 0;
+  if constexpr (32 * CELLS <= 224) {
+    const int64_t want = (static_cast<int64_t>(a.chunk < a.n ? a.chunk : a.n) + 15) / 16 * 16;
+    if (want <= 4096) light_tab = static_cast<int>(want);
+  }
+  auto launch_light = [&](auto kernel, int tab_bytes) -> bool {
+    const int dyn = tab_bytes * S_WARPS;
+    int per_sm = 0;
+    CSG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, S_THREADS, dyn));
+    if (per_sm < 1) per_sm = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctx.num_sms * per_sm);
+    cfg.blockDim = dim3(S_THREADS);
+    cfg.dynamicSmemBytes = dyn;
+    cfg.stream = ctx.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CSG_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, 1, tab_bytes));
+    return true;
+  };
+  if constexpr (32 * CELLS <= 224) {
+    if (light_tab > 0) {
+      if (!launch_light(sketch_kernel<CELLS, true>, light_tab)) return false;
+    } else if (!launch_light(sketch_kernel<CELLS, false>, 0)) {
+      return false;
+    }
+  } else if (!launch_light(sketch_kernel<CELLS, false>, 0)) {
+    return false;
+  }
   heavy_topk_kernel<CELLS><<<ctx.num_sms, S_THREADS, 0, ctx.stream>>>(a);
   CSG_CUDA(cudaGetLastError());
   count_launches(7);
