@@ -218,6 +218,19 @@ struct Sketch {
     }
   }
 
+  // this lane's smallest (weight, cell): all the victim search of the table steps needs
+  __device__ __forceinline__ void lane_min() {
+    l1w = __float_as_uint(w[0]);
+    l1c = 0;
+#pragma unroll
+    for (int c = 1; c < CELLS; ++c) {
+      const uint32_t x = __float_as_uint(w[c]);
+      const bool first = x < l1w;
+      l1w = first ? x : l1w;
+      l1c = first ? c : l1c;
+    }
+  }
+
   // ---- steps with a key -> slot table --------------------------------------------------
   // One byte per row of the chunk in shared memory (0 = not in the sketch, else slot + 1)
   // answers "is the key there, and where" with one broadcast load instead of CELLS compares
@@ -234,7 +247,7 @@ struct Sketch {
     put(filled, s, a);
     if (lane == 0) tab[s - cbase] = static_cast<uint8_t>(filled + 1);
     ++filled;
-    if (filled == 32 * CELLS) lane_top2();
+    if (filled == 32 * CELLS) lane_min();
     __syncwarp();
   }
 
@@ -242,7 +255,7 @@ struct Sketch {
     const int q = tab[s - cbase];
     if (q) {  // hit
       add_weight(q - 1, a);
-      lane_top2();
+      lane_min();
       return;
     }
     find_victim(l1w, l1c, gmin, gown, gcell);
@@ -256,7 +269,7 @@ struct Sketch {
       tab[s - cbase] = static_cast<uint8_t>(gslot + 1);
     }
     put(gslot, s, wnew);
-    lane_top2();
+    lane_min();
     __syncwarp();
   }
 

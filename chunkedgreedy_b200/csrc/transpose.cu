@@ -129,7 +129,7 @@ __device__ void radix_pass(const uint32_t *kin, const PayT *pin, uint32_t *kout,
       else
         pay[i] = valid ? pin[idx] : PayT(0);
       const uint32_t d = valid ? ((key[i] >> shift) & 255u) : 256u;
-      const unsigned peers = __match_any_sync(FULL, d);
+      const unsigned peers = match_digit(d);
       const int leader = __ffs(peers) - 1;
       uint32_t pre = 0;
       if (lane == leader && valid) {
@@ -450,7 +450,7 @@ __global__ void __launch_bounds__(T_THREADS) heavy_scatter_kernel(TransposeArgs 
       key[i] = valid ? kin[idx] : 0u;
       pay[i] = ps == 0 ? static_cast<uint32_t>(r.off + idx) : (valid ? pin[idx] : 0u);
       const uint32_t d = valid ? ((key[i] >> shift) & 255u) : 256u;
-      const unsigned peers = __match_any_sync(FULL, d);
+      const unsigned peers = match_digit(d);
       const int leader = __ffs(peers) - 1;
       uint32_t pre = 0;
       if (lane == leader && valid) {
