@@ -256,6 +256,7 @@ def run_reference(args, rank, world):
 def workload_config(n, nnz, k, args):
     names = {"rmat22": "rmat scale %d ef16 a.57 b.19 c.19 d.05 dedup seed3" % args.scale,
              "zipf65k": "zipf-banded 65536 rows seed0", "stencil1024": "9-point stencil 1024^2 relabelled seed1",
+             "stencil1024nat": "9-point stencil 1024^2 natural order seed1",
              "road2m": "road lattice 2M vertices relabelled seed2",
              "rmat20gcn": "rmat scale 20 symmetrised + self loops, normalised, seed4"}
     return {"workload": "%s; csg k=%d M=%d chunk=%d"
@@ -701,7 +702,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--scale", type=int, default=22, help="R-MAT scale (22 = the named workload)")
     ap.add_argument("--workload", default="rmat22",
-                    choices=["rmat22", "zipf65k", "stencil1024", "road2m", "rmat20gcn"],
+                    choices=["rmat22", "zipf65k", "stencil1024", "stencil1024nat", "road2m", "rmat20gcn"],
                     help="rmat22 is the bench workload; the others are the remaining configurations")
     ap.add_argument("--gcn", action="store_true",
                     help="also run the reorder-then-train GCN experiment (use with --workload rmat20gcn)")

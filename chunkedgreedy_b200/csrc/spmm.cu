@@ -113,10 +113,9 @@ struct Step {
 
 // FMA of up to U nonzeros [p, p + cnt) of one row into acc, for the panels
 // pn0 .. pn0 + PAN - 1, all loads of a kind issued together.
-template <int G, int VEC, int PAN>
+template <int G, int VEC, int PAN, int U = Step<PAN>::U>
 __device__ __forceinline__ void fma_step(const SpmmArgs &a, int32_t p, int cnt, int32_t col0,
                                          float (&acc)[PAN][VEC]) {
-  constexpr int U = Step<PAN>::U;
   int32_t c[U];
   float x[U];
   float b[U][PAN][VEC];
@@ -258,6 +257,12 @@ __global__ void __launch_bounds__(M_THREADS, M_BLOCKS_PER_SM) spmm_rows_kernel(S
       const int cnt = pe - p < U ? pe - p : U;
       fma_step<G, VEC, PAN>(a, p, cnt, pn0 * (G * VEC) + gl * VEC, acc);
       p += cnt;
+      // a short tail (a row of nine nonzeros is a full step and one more) goes along in the
+      // same turn of the loop: the turn, with its hand-out of rows, costs more than the tail
+      if (pe - p > 0 && pe - p <= U / 2) {
+        fma_step<G, VEC, PAN, U / 2>(a, p, pe - p, pn0 * (G * VEC) + gl * VEC, acc);
+        p = pe;
+      }
     }
   }
 }

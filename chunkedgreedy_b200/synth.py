@@ -257,6 +257,8 @@ WORKLOADS = {
     # name: (generator, kwargs, is_symmetric, dense widths for SpMM)
     "zipf65k": (zipf_banded, dict(n=65536, seed=0), False, (32,)),
     "stencil1024": (stencil9, dict(side=1024, seed=1), True, (32, 128)),
+    # the same stencil in its natural (row-major grid) order: an input whose gathers hit the cache
+    "stencil1024nat": (stencil9, dict(side=1024, seed=1, relabel=False), True, (32, 128)),
     "road2m": (road_lattice, dict(n=2_000_000, seed=2), True, (64,)),
     "rmat22": (rmat, dict(scale=22, edge_factor=16, seed=3), False, (32, 128, 256)),
     "rmat20gcn": (rmat_gcn, dict(scale=20, edge_factor=16, seed=4), True, (128, 16)),
