@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libsporder_b200.so")
+# SPORDER_B200_LIBRARY names another build of the same library (the checked build)
+LIB_PATH = os.environ.get("SPORDER_B200_LIBRARY") or os.path.join(HERE, "libsporder_b200.so")
 
 _lib = None
 

@@ -185,6 +185,17 @@ bool finish_call(Context &ctx, const CsgScratch &s) {
   CSG_CUDA(cudaGetLastError());
   CSG_REQUIRE(h[CTRL_BAD_INPUT] == 0,
               "malformed CSR: row pointers must be non-decreasing inside [0, nnz] (results unspecified)");
+  if (h[CTRL_CHECK] != 0) {  // only a build with -DSPORDER_CHECKED writes this word
+    static const char *const site[] = {"?", "cand[] index of a group", "position in a stream ring",
+                                       "stream offset of a heavy row", "stream key outside its chunk",
+                                       "heavy-row state item", "row of the top-k table", "row list entry",
+                                       "order[] position", "scatter position of a radix pass",
+                                       "group position written by the transpose", "part table entry"};
+    const uint32_t k = h[CTRL_CHECK] < sizeof(site) / sizeof(site[0]) ? h[CTRL_CHECK] : 0;
+    const long long idx = static_cast<long long>((static_cast<uint64_t>(h[CTRL_CHECK + 2]) << 32) | h[CTRL_CHECK + 1]);
+    set_error("checked build: index out of bounds (%s: %lld); results unspecified", site[k], idx);
+    return false;
+  }
   CSG_REQUIRE(h[CTRL_STREAM_OVERRUN] == 0,
               "internal: a heavy row's stream slice did not fit its place in the stream buffer");
   uint64_t need = (static_cast<uint64_t>(h[CTRL_HEAVY_NEED + 1]) << 32) | h[CTRL_HEAVY_NEED];

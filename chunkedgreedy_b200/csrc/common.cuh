@@ -118,6 +118,7 @@ enum {
   CTRL_HEAVY_PARTS = 9,    // column slices of the heavy rows
   CTRL_HEAVY_NEED = 10,    // and the word after it: stream elements of all rows of heavy weight (64-bit)
   CTRL_STREAM_OVERRUN = 12,  // set by heavy_expand_kernel when a slice would pass the stream buffer
+  CTRL_CHECK = 13,         // checked build: site of the first index out of bounds, then the index (64-bit)
   CTRL_BUCKET_COUNT = 16,  // 33 entries
   CTRL_BUCKET_BASE = 56,   // 33 entries
   CTRL_BUCKET_FILL = 96,   // 33 entries
@@ -155,6 +156,40 @@ bool launch_spmm(Context &ctx, int32_t n, int32_t nnz, int32_t w, const int32_t 
 #ifdef __CUDACC__
 constexpr unsigned FULL = 0xFFFFFFFFu;
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
+
+// ---- checked build ----------------------------------------------------------------------
+// Compiled with -DSPORDER_CHECKED (python -m chunkedgreedy_b200.build --checked) every index
+// that a kernel derives from data another kernel wrote - positions in the transposed chunk,
+// stream offsets, table slots, list entries - is tested before use; the first one out of
+// bounds is recorded (site, index) and the access is skipped, so the kernel runs on with
+// harmless values and the host reports the site instead of the GPU faulting.  This stands in
+// for compute-sanitizer on machines where that tool may not be run.  In the normal build the
+// test is a constant `true` and costs nothing.
+enum CheckSite : uint32_t {
+  CHK_CAND = 1,      // cand[] index from a group descriptor
+  CHK_RING = 2,      // position in a warp's stream ring
+  CHK_STREAM = 3,    // hstream[] offset of a heavy row
+  CHK_KEY = 4,       // stream key outside its chunk (key -> slot table)
+  CHK_STATE = 5,     // heavy_state[] / heavy_off[] item
+  CHK_TABLE = 6,     // row of the top-k table
+  CHK_LIST = 7,      // row_list[] entry
+  CHK_ORDER = 8,     // order[] position in the greedy stage
+  CHK_SORT = 9,      // scatter position of a radix pass
+  CHK_GROUP = 10,    // group start / position written by the transpose
+  CHK_PART = 11,     // part_off[] / part_base[] entry
+};
+#ifdef SPORDER_CHECKED
+__device__ __forceinline__ bool index_ok(uint32_t *ctrl, uint32_t site, long long idx, long long bound) {
+  if (idx >= 0 && idx < bound) return true;
+  if (atomicCAS(&ctrl[CTRL_CHECK], 0u, site) == 0u) {
+    ctrl[CTRL_CHECK + 1] = static_cast<uint32_t>(static_cast<unsigned long long>(idx));
+    ctrl[CTRL_CHECK + 2] = static_cast<uint32_t>(static_cast<unsigned long long>(idx) >> 32);
+  }
+  return false;
+}
+#else
+__device__ __forceinline__ bool index_ok(uint32_t *, uint32_t, long long, long long) { return true; }
+#endif
 
 // counter += v, sticking at 0xFFFFFFFF instead of wrapping.  Whoever sees the sum wrap puts
 // the ceiling back; the last operation on a counter that ever wrapped is such a repair, so

@@ -25,6 +25,7 @@ struct GreedyArgs {
   const uint32_t *row_work;
   int32_t *order;
   uint32_t *ctrl;      // stats block, or nullptr
+  uint32_t *ctrl_all;  // the control words (checked build: where a bad index is recorded)
   uint32_t *gbitmaps;  // global bitmaps when a chunk's bitmaps do not fit shared memory
   int32_t words;       // bitmap words per chunk
 };
@@ -71,7 +72,8 @@ __global__ void __launch_bounds__(G_WARPS * 32) greedy_kernel(GreedyArgs a) {
     if (lane == 0) visited[loc >> 5] |= 1u << (loc & 31);
     if (lane == (emitted & 31)) mine = cur + a.row_base;
     ++emitted;
-    if ((emitted & 31) == 0) a.order[start + emitted - 32 + lane] = mine;
+    if ((emitted & 31) == 0 && index_ok(a.ctrl_all, CHK_ORDER, emitted, size + 1))
+      a.order[start + emitted - 32 + lane] = mine;
     __syncwarp();
 
     int32_t best_c = -1;
@@ -146,7 +148,8 @@ __global__ void __launch_bounds__(G_WARPS * 32) greedy_kernel(GreedyArgs a) {
         while (take) {
           const int b = __ffs(take) - 1;
           take &= take - 1;
-          a.order[at++] = start + (w << 5) + b + a.row_base;
+          if (index_ok(a.ctrl_all, CHK_ORDER, at - start, size)) a.order[at] = start + (w << 5) + b + a.row_base;
+          ++at;
         }
         emitted += total;
         restarts += total;
@@ -258,6 +261,7 @@ bool launch_greedy(Context &ctx, int32_t n, const CsgParams &p, CsgScratch &s,
   a.row_work = s.row_work;
   a.order = d_new_order;
   a.ctrl = with_stats ? s.ctrl : nullptr;
+  a.ctrl_all = s.ctrl;
   const int32_t span = p.chunk < n ? p.chunk : n;
   a.words = (span + 31) / 32;
   size_t smem = static_cast<size_t>(G_WARPS) * 2 * a.words * sizeof(uint32_t);

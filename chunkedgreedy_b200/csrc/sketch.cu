@@ -365,6 +365,11 @@ struct Producer {
 
   __device__ __forceinline__ Producer(const SketchArgs &args) : a(args) {}
 
+  // cand[idx], idx from a group descriptor the transpose wrote (checked build: tested)
+  __device__ __forceinline__ int2 cand_at(int32_t idx) const {
+    return index_ok(a.ctrl, CHK_CAND, idx, a.nnz) ? a.cand[idx] : make_int2(r, 1);
+  }
+
   __device__ __forceinline__ void load_next(int32_t p) {
     nsg = make_int2(0, 0);
     nrank = 0;
@@ -394,7 +399,7 @@ struct Producer {
 
   // entry q of this lane's group with the row itself skipped -> (row, alpha)
   __device__ __forceinline__ void emit(int32_t q, int32_t *ring_s, float *ring_a, int32_t at) const {
-    const int2 e = a.cand[gst + q + (q >= grank ? 1 : 0)];
+    const int2 e = cand_at(gst + q + (q >= grank ? 1 : 0));
     ring_s[at] = e.x;
     ring_a[at] = 2.0f / static_cast<float>(rs + e.y);
   }
@@ -428,12 +433,12 @@ struct Producer {
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int32_t q = g_done + i0 + u * 32 + lane;
-            if (i0 + u * 32 + lane < take) e[u] = a.cand[g_st + q + (q >= g_rank ? 1 : 0)];
+            if (i0 + u * 32 + lane < take) e[u] = cand_at(g_st + q + (q >= g_rank ? 1 : 0));
           }
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int32_t i = i0 + u * 32 + lane;
-            if (i < take) {
+            if (i < take && index_ok(a.ctrl, CHK_RING, fill + i, RING)) {
               ring_s[fill + i] = e[u].x;
               ring_a[fill + i] = 2.0f / static_cast<float>(rs + e[u].y);
             }
@@ -467,23 +472,25 @@ struct Producer {
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
             const int32_t q = done + i + u;
-            e[u] = a.cand[gst + q + (q >= grank ? 1 : 0)];
+            e[u] = cand_at(gst + q + (q >= grank ? 1 : 0));
           }
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
-            ring_s[at0 + i + u] = e[u].x;
-            ring_a[at0 + i + u] = 2.0f / static_cast<float>(rs + e[u].y);
+            if (index_ok(a.ctrl, CHK_RING, at0 + i + u, RING)) {
+              ring_s[at0 + i + u] = e[u].x;
+              ring_a[at0 + i + u] = 2.0f / static_cast<float>(rs + e[u].y);
+            }
           }
         }
         int2 e[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
           const int32_t q = done + i + u;
-          if (i + u < take) e[u] = a.cand[gst + q + (q >= grank ? 1 : 0)];
+          if (i + u < take) e[u] = cand_at(gst + q + (q >= grank ? 1 : 0));
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-          if (i + u < take) {
+          if (i + u < take && index_ok(a.ctrl, CHK_RING, at0 + i + u, RING)) {
             ring_s[at0 + i + u] = e[u].x;
             ring_a[at0 + i + u] = 2.0f / static_cast<float>(rs + e[u].y);
           }
@@ -520,13 +527,19 @@ __device__ __forceinline__ void consume(Sketch<CELLS> &sk, const int32_t *bs, co
 }
 
 // The same with the key -> slot table (see Sketch::add_full_tab).
+// A stream key as an index into a table over the chunk's rows: in the checked build a key
+// outside the chunk is recorded and replaced by the chunk's first row.
+__device__ __forceinline__ int32_t key_in_chunk(uint32_t *ctrl, int32_t s, int32_t cbase, int32_t span) {
+  return index_ok(ctrl, CHK_KEY, static_cast<long long>(s) - cbase, span) ? s : cbase;
+}
+
 template <int CELLS>
 __device__ __forceinline__ void consume_tab(Sketch<CELLS> &sk, uint8_t *tab, int32_t cbase, const int32_t *bs,
-                                            const float *ba, int cnt) {
+                                            const float *ba, int cnt, uint32_t *ctrl, int32_t span) {
   int t = 0;
-  for (; t < cnt && sk.filled < 32 * CELLS; ++t) sk.add_filling_tab(bs[t], ba[t], tab, cbase);
+  for (; t < cnt && sk.filled < 32 * CELLS; ++t) sk.add_filling_tab(key_in_chunk(ctrl, bs[t], cbase, span), ba[t], tab, cbase);
 #pragma unroll 1
-  for (; t < cnt; ++t) sk.add_full_tab(bs[t], ba[t], tab, cbase);
+  for (; t < cnt; ++t) sk.add_full_tab(key_in_chunk(ctrl, bs[t], cbase, span), ba[t], tab, cbase);
 }
 
 __device__ __forceinline__ bool row_bounds_ok(const SketchArgs &a, int32_t rb, int32_t re) {
@@ -564,6 +577,7 @@ __global__ void __launch_bounds__(S_THREADS) sketch_kernel(SketchArgs a, int aft
     item = __shfl_sync(FULL, item, 0);
     if (item >= listed) break;
     const int32_t r = a.row_list[item];
+    if (!index_ok(a.ctrl, CHK_LIST, r, a.n)) continue;
     const int32_t rb = a.ptr[r], re = a.ptr[r + 1];
     if (!row_bounds_ok(a, rb, re)) continue;
     const int32_t cbase = (r / a.chunk) * a.chunk;
@@ -573,7 +587,7 @@ __global__ void __launch_bounds__(S_THREADS) sketch_kernel(SketchArgs a, int aft
       const int cnt = prod.produce(bs, ba);
       if (cnt == 0) break;
       if (TAB)
-        consume_tab<CELLS>(sk, tab, cbase, bs, ba, cnt);
+        consume_tab<CELLS>(sk, tab, cbase, bs, ba, cnt, a.ctrl, tab_bytes);
       else
         consume<CELLS>(sk, bs, ba, cnt);
       __syncwarp();
@@ -747,6 +761,7 @@ __global__ void __launch_bounds__(S_THREADS) heavy_expand_kernel(SketchArgs a) {
     if (part >= parts) break;
     const PartRef p = part_ref(a, part, heavy);
     if (p.pe <= p.pb) continue;
+    if (!index_ok(a.ctrl, CHK_LIST, p.r, a.n)) continue;
     uint32_t at = a.part_off[part];
     int2 *out = a.hstream + at;
     prod.begin(p.r, p.pb, p.pe, p.row_size);
@@ -873,7 +888,23 @@ struct RoundState {
   int32_t sk[M];                 // ... and keys
   int32_t miss_pos[32];          // lane of the i-th miss of the window
   uint32_t fence_sink;           // see phase_fence
+#ifdef SPORDER_CHECKED
+  uint32_t *ctrl;                // checked build: where a key outside its chunk is recorded ...
+  int32_t span;                  // ... and the rows the key tables cover
+#endif
 };
+
+// The key of a stream element as the rounds use it: in the checked build a key outside the
+// chunk's table is recorded and replaced by the chunk's first row.
+template <int CELLS, bool TAB>
+__device__ __forceinline__ int32_t round_key(const RoundState<CELLS> &st, int32_t s, int32_t cbase) {
+#ifdef SPORDER_CHECKED
+  if (TAB) return key_in_chunk(st.ctrl, s, cbase, st.span);
+#endif
+  (void)st;
+  (void)cbase;
+  return s;
+}
 
 // Slot that holds key s, or -1.  With TAB from the key -> slot table of the chunk (one byte
 // per row); without it - chunks whose tables would not fit shared memory - by comparing s
@@ -914,7 +945,7 @@ __device__ __forceinline__ int round_full(RoundState<CELLS> &st, uint8_t *tab, i
   phase_fence(sink);
   const bool valid = p + lane < cnt;
   const int2 elem = valid ? ring[p + lane] : make_int2(0, 0);
-  const int32_t s = elem.x;
+  const int32_t s = round_key<CELLS, TAB>(st, elem.x, cbase);
   const float al = __int_as_float(elem.y);
   uint32_t mine[CELLS];
   int32_t mykey[CELLS];
@@ -1056,7 +1087,7 @@ __device__ __forceinline__ int round_window(RoundState<CELLS> &st, uint8_t *tab,
   WINDOW_FENCE(sink);
   const bool valid = p + lane < cnt;
   const int2 elem = valid ? ring[p + lane] : make_int2(0, 0);
-  const int32_t s = elem.x;
+  const int32_t s = round_key<CELLS, TAB>(st, elem.x, cbase);
   const float al = __int_as_float(elem.y);
   // Lanes that carry the same key: every lane sets its bit in a word of shared memory under
   // its key and reads the word back (cleared again at the end of the round).  match.any, the
@@ -1215,7 +1246,7 @@ __device__ __forceinline__ int round_fill(RoundState<CELLS> &st, uint8_t *tab, i
   const uint32_t below = (1u << lane) - 1u;
   const bool valid = p + lane < cnt;
   const int2 elem = valid ? ring[p + lane] : make_int2(0, 0);
-  const int32_t s = elem.x;
+  const int32_t s = round_key<CELLS, TAB>(st, elem.x, cbase);
   const float al = __int_as_float(elem.y);
   const int q = valid ? slot_of<CELLS, TAB>(st, tab, cbase, s) : 0;
   const bool miss = valid && q < 0;
@@ -1398,6 +1429,13 @@ __global__ void __launch_bounds__(S_THREADS, 1) heavy_rounds_kernel(SketchArgs a
                               static_cast<size_t>(warp) * mates_words
                         : nullptr;
   for (int i = lane; i < mates_words; i += 32) mates[i] = 0u;
+#ifdef SPORDER_CHECKED
+  if (lane == 0) {
+    state[warp].ctrl = a.ctrl;
+    state[warp].span = tab_bytes;
+  }
+  __syncwarp();
+#endif
   for (int i = lane * 16; i < tab_bytes; i += 32 * 16) *reinterpret_cast<uint4 *>(tab + i) = make_uint4(0, 0, 0, 0);
   for (;;) {
     uint32_t item = 0;
@@ -1405,6 +1443,11 @@ __global__ void __launch_bounds__(S_THREADS, 1) heavy_rounds_kernel(SketchArgs a
     item = __shfl_sync(FULL, item, 0);
     if (item >= heavy) break;
     const int32_t r = a.row_list[item];
+    // checked build: the row, its place in the state array and its stream's extent
+    if (!index_ok(a.ctrl, CHK_LIST, r, a.n) || !index_ok(a.ctrl, CHK_STATE, item, a.heavy_max) ||
+        !index_ok(a.ctrl, CHK_STREAM, static_cast<long long>(a.heavy_off[item]) + a.row_work[r],
+                  static_cast<long long>(a.stream_cap) + 1))
+      continue;
     int32_t *out = a.heavy_state + static_cast<size_t>(item) * (2 * CELLS * 32);
 #ifdef CSG_ROUND_PROFILE
     const unsigned long long row_t0 = clock64();

@@ -85,7 +85,7 @@ struct Shared {
 // column array and uses the position as payload.
 template <typename PayT, bool FIRST>
 __device__ void radix_pass(const uint32_t *kin, const PayT *pin, uint32_t *kout, PayT *pout,
-                           int L, int shift, Shared &sh) {
+                           int L, int shift, Shared &sh, uint32_t *ctrl) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid < 256) sh.hist[tid] = 0;
   __syncthreads();
@@ -158,8 +158,10 @@ __device__ void radix_pass(const uint32_t *kin, const PayT *pin, uint32_t *kout,
       if (idx < L) {
         const uint32_t d = (key[i] >> shift) & 255u;
         const uint32_t dst = sh.wc[warp * 256 + d] + rk[i];
-        kout[dst] = key[i];
-        pout[dst] = pay[i];
+        if (index_ok(ctrl, CHK_SORT, dst, L)) {
+          kout[dst] = key[i];
+          pout[dst] = pay[i];
+        }
       }
     }
     __syncthreads();
@@ -237,6 +239,7 @@ __device__ void emit_groups(const uint32_t *K, const PayT *P, uint32_t *S, PayT 
   for (int i = tid; i < L; i += T_THREADS) {
     const int32_t p = static_cast<int32_t>(P[i]);
     const int32_t st = static_cast<int32_t>(S[i]);
+    if (!index_ok(a.ctrl, CHK_GROUP, p, L) || !index_ok(a.ctrl, CHK_GROUP, st, L)) continue;
     const int32_t len = static_cast<int32_t>(LN[st]);
     int32_t row;
     if (rows_in_smem)
@@ -281,10 +284,10 @@ __global__ void __launch_bounds__(T_THREADS, 1) transpose_kernel(TransposeArgs a
     __syncthreads();
     const uint32_t *kin0 = reinterpret_cast<const uint32_t *>(a.ind + b);
     const int P = a.passes;
-    radix_pass<uint16_t, true>(kin0, nullptr, sh.skey[0], sh.spay[0], L, 0, sh);
+    radix_pass<uint16_t, true>(kin0, nullptr, sh.skey[0], sh.spay[0], L, 0, sh, a.ctrl);
     for (int ps = 1; ps < P; ++ps)
       radix_pass<uint16_t, false>(sh.skey[(ps - 1) & 1], sh.spay[(ps - 1) & 1], sh.skey[ps & 1],
-                                  sh.spay[ps & 1], L, 8 * ps, sh);
+                                  sh.spay[ps & 1], L, 8 * ps, sh, a.ctrl);
     const int f = (P - 1) & 1;
     emit_groups<uint16_t>(sh.skey[f], sh.spay[f], sh.skey[f ^ 1], sh.spay[f ^ 1], L, b, cs, rows,
                           rows_in_smem, a, sh);
@@ -479,8 +482,10 @@ __global__ void __launch_bounds__(T_THREADS) heavy_scatter_kernel(TransposeArgs 
       if (idx < r.cnt) {
         const uint32_t d = (key[i] >> shift) & 255u;
         const uint32_t dst = wc[warp * 256 + d] + rk[i];
-        kout[dst] = key[i];
-        pout[dst] = pay[i];
+        if (index_ok(a.ctrl, CHK_SORT, dst, r.L)) {
+          kout[dst] = key[i];
+          pout[dst] = pay[i];
+        }
       }
     }
     __syncthreads();
@@ -539,6 +544,7 @@ __global__ void __launch_bounds__(T_THREADS) heavy_emit_kernel(TransposeArgs a) 
       }
       const int32_t len = lo - st;
       const int32_t p = static_cast<int32_t>(P[i]);
+      if (!index_ok(a.ctrl, CHK_GROUP, p, r.L)) continue;
       int32_t row, rl;
       if (staged) {
         const int32_t lr = row_of(sptr, 0, r.rows, r.b + p);

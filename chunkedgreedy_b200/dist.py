@@ -146,18 +146,24 @@ def chunk_similarity_greedy_sharded(ptr, ind, *, k=0, oversampling=0.0, chunk_si
     return gather_shards(local, bounds, group)
 
 
+SPMM_ROW_COST = 4  # what a row costs the SpMM kernel beside its nonzeros, in nonzeros
+
+
 def spmm_row_bounds(ptr, world_size):
     """Contiguous row ranges ``[(r0, r1), ...]`` for the row-partitioned SpMM, one per rank,
-    balanced by nonzeros (no chunk alignment: SpMM rows are independent).  ``ptr`` may be a
-    numpy array or a (host or device) torch tensor."""
+    balanced by the kernel's own cost measure, nonzeros plus ``SPMM_ROW_COST`` per row (no
+    chunk alignment: SpMM rows are independent; balancing nonzeros alone gives the rank with
+    the hub rows too little and the rank with the many short rows too much to do).  ``ptr``
+    may be a numpy array or a (host or device) torch tensor."""
     if hasattr(ptr, "detach"):
         ptr = ptr.detach().cpu().numpy()
     ptr = np.asarray(ptr)
     n = ptr.size - 1
-    total = int(ptr[-1])
+    cost = ptr.astype(np.int64) + SPMM_ROW_COST * np.arange(n + 1, dtype=np.int64)
+    total = int(cost[-1])
     cuts = [0]
     for r in range(1, world_size):
-        c = int(np.searchsorted(ptr, total * r / world_size, side="left"))
+        c = int(np.searchsorted(cost, total * r / world_size, side="left"))
         cuts.append(min(max(c, cuts[-1]), n))
     cuts.append(n)
     return [(cuts[i], cuts[i + 1]) for i in range(world_size)]

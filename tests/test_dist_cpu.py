@@ -94,8 +94,8 @@ def test_spmm_row_bounds_cover_and_balance():
         b = csgdist.spmm_row_bounds(ptr, world)
         assert len(b) == world and b[0][0] == 0 and b[-1][1] == n
         assert all(a1 == b0 for (_, a1), (b0, _) in zip(b, b[1:]))
-        nnz = [int(ptr[r1] - ptr[r0]) for r0, r1 in b]
-        assert max(nnz) <= 1.2 * (sum(nnz) / world) + 4096
+        cost = [int(ptr[r1] - ptr[r0]) + csgdist.SPMM_ROW_COST * (r1 - r0) for r0, r1 in b]
+        assert max(cost) <= 1.2 * (sum(cost) / world) + 4096 + csgdist.SPMM_ROW_COST
     # more ranks than rows: the extra ranks get empty ranges
     b = csgdist.spmm_row_bounds(np.array([0, 2, 3], dtype=np.int32), 5)
     assert b[0][0] == 0 and b[-1][1] == 2 and sum(r1 - r0 for r0, r1 in b) == 2
