@@ -872,9 +872,15 @@ __global__ void __launch_bounds__(S_THREADS, 1) heavy_consume_kernel(SketchArgs 
 
 constexpr int H_RING = 1024;    // stream elements staged per batch
 constexpr int ROUND_CELLS = 4;  // largest sketch (cells per lane) resolved in rounds
-constexpr int WINDOW_PAYS = 18;    // elements whole-window rounds must resolve on average to beat strict rounds
-constexpr int WINDOW_RETRY = 24;   // the mean a row starts from when it tries the window again
-constexpr int STRICT_ROUNDS = 48;  // strict rounds in between
+// Whole-window rounds and the table steps of the light rows are used for sketches of 64 slots
+// (two cells per lane: k = 16 at the default oversampling, the benchmark's configuration).
+// With 128 slots both measured slower on the R-MAT GCN configuration (sketch stage 55.5 ms
+// without either, 62.4 with the whole-window rounds, 65.3 with the table steps, 72.0 with
+// both): the ranking of a round grows with the square of the sketch, and a step's work per
+// lane with its cells.  With 32 slots a window of 32 can take every entry.
+constexpr int WINDOW_CELLS = 2;
+constexpr int TRIAL_ROUNDS = 8;     // rounds of each kind a row times before it settles on one ...
+constexpr int COMMIT_ROUNDS = 160;  // ... for this many rounds
 constexpr int ROUND_RING_BYTES = S_WARPS * 2 * H_RING * 8;
 
 template <int CELLS>
@@ -1288,42 +1294,18 @@ __device__ __forceinline__ void stage_batch(int2 *ring, const int2 *in, int cnt,
   asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
-// The two kinds of round on a full sketch as functions of their own (like rounds_row below:
-// compiled into one body, each kind loses a third of its speed to the other's registers and
-// schedule).  Strict rounds on [p, cnt) of a batch, at most `left` of them.
+// The whole-window rounds as a function of their own (like rounds_row below: compiled into one
+// body with the strict rounds, each kind loses speed to the other's registers and schedule).
+// Whole-window rounds on [p, cnt) of a batch, at most `left` of them.
 template <int CELLS, bool TAB>
-__device__ __noinline__ int strict_rounds(RoundState<CELLS> &st, uint8_t *tab, int32_t cbase,
-                                          const int2 *ring, int p, int cnt, int &left) {
+__device__ __noinline__ int window_rounds(RoundState<CELLS> &st, uint8_t *tab, uint32_t *mates,
+                                          int32_t cbase, const int2 *ring, int p, int cnt, int &left,
+                                          unsigned long long *prof) {
   const int lane = lane_id();
   uint32_t sink = 0;
   while (p < cnt && left > 0) {
-    p += round_full<CELLS, TAB>(st, tab, cbase, ring, p, cnt, lane, sink);
+    p += round_window<CELLS, TAB>(st, tab, mates, cbase, ring, p, cnt, lane, sink, prof);
     --left;
-  }
-  if (lane == 0) st.fence_sink = sink;
-  return p;
-}
-
-// Whole-window rounds on [p, cnt) of a batch until the running mean of what they resolve
-// (mean4: four times the mean) falls below WINDOW_PAYS; then `left` strict rounds are due.
-template <int CELLS, bool TAB>
-__device__ __noinline__ int window_rounds(RoundState<CELLS> &st, uint8_t *tab, uint32_t *mates,
-                                          int32_t cbase, const int2 *ring, int p, int cnt, int &mean4,
-                                          int &left, unsigned long long *prof) {
-  const int lane = lane_id();
-  uint32_t sink = 0;
-  while (p < cnt) {
-    const int got = round_window<CELLS, TAB>(st, tab, mates, cbase, ring, p, cnt, lane, sink, prof);
-    const bool whole = p + got < cnt;  // (a window cut short by the end of a batch says nothing)
-    p += got;
-    if (whole) {
-      mean4 = mean4 - (mean4 >> 2) + got;
-      if (mean4 < 4 * WINDOW_PAYS) {
-        left = STRICT_ROUNDS;
-        mean4 = 4 * WINDOW_RETRY;
-        break;
-      }
-    }
   }
   if (lane == 0) st.fence_sink = sink;
   return p;
@@ -1346,11 +1328,17 @@ __device__ __noinline__ void rounds_row(const int2 *in, uint32_t total, int32_t 
     st.key[c * 32 + lane] = -1;
     st.w[c * 32 + lane] = 0u;
   }
+  int filled = 0, buf = 0;
+  // (see the loop below) kind of round in use, rounds left in the stretch, the trial being
+  // booked (0 window, 1 strict, -1 none), and what the trials resolved in how many cycles
 #ifdef CSG_STRICT_ONLY
-  int filled = 0, buf = 0, strict_left = 1 << 30, mean4 = 4 * 32;
+  int mode = 1, left = 1 << 30, trial = -1;
 #else
-  int filled = 0, buf = 0, strict_left = 0, mean4 = 4 * 32;
+  int mode = 0, left = TRIAL_ROUNDS, trial = 0;
+
 #endif
+  long long got[2] = {0, 0}, took[2] = {0, 0};
+  int streak = 0, last_mode = -1;
   uint32_t sink = 0;
   __syncwarp();
   stage_batch(ring0, in, static_cast<int>(total < H_RING ? total : H_RING), lane);
@@ -1366,32 +1354,55 @@ __device__ __noinline__ void rounds_row(const int2 *in, uint32_t total, int32_t 
     const int2 *ring = buf ? ring1 : ring0;
     int p = 0;
     while (p < cnt && filled < M) p += round_fill<CELLS, TAB>(st, tab, cbase, ring, p, cnt, lane, filled);
-    if constexpr (CELLS >= 2) {
-      // A whole-window round costs half as much again as a strict one and pays where it
-      // resolves (nearly) the whole window: rows whose own length dominates their Dice terms.
-      // Where the terms vary widely, entries put back light are taken again at once, either
-      // kind of round ends after a few elements and the cheaper one wins.  The row decides by
-      // a running mean of what its whole-window rounds resolve: below WINDOW_PAYS the next
-      // STRICT_ROUNDS rounds are strict ones, then the window is tried again.
+    if constexpr (CELLS == WINDOW_CELLS) {
+      // Which kind of round is faster depends on the row: a whole-window round costs more and
+      // pays where it resolves (nearly) the whole window - rows whose own length dominates their
+      // Dice terms.  Where the terms vary widely, entries put back light are taken again at
+      // once, either kind ends after a few elements and the cheaper one wins; and how often a
+      // strict round is cut short depends on the sketch size.  So the row measures: a few
+      // rounds of each kind against the clock, then a long stretch of the kind that resolved
+      // more elements per cycle, and again.
       while (p < cnt) {
-        if (strict_left > 0) {
-          p = strict_rounds<CELLS, TAB>(st, tab, cbase, ring, p, cnt, strict_left);
-          continue;
+        const int before = p;
+        const long long t0 = clock64();
+        if (mode == 0) {
+          p = window_rounds<CELLS, TAB>(st, tab, mates, cbase, ring, p, cnt, left, prof);
+        } else {  // (in line: as a function of its own this kind runs a tenth slower)
+          while (p < cnt && left > 0) {
+            p += round_full<CELLS, TAB>(st, tab, cbase, ring, p, cnt, lane, sink);
+            --left;
+          }
         }
-        const int got = round_window<CELLS, TAB>(st, tab, mates, cbase, ring, p, cnt, lane, sink, prof);
-        const bool whole = p + got < cnt;  // (a window cut short by the end of a batch says nothing)
-        p += got;
-        if (whole) {
-          mean4 = mean4 - (mean4 >> 2) + got;
-          if (mean4 < 4 * WINDOW_PAYS) {
-            strict_left = STRICT_ROUNDS;
-            mean4 = 4 * WINDOW_RETRY;
+        if (trial >= 0) {  // a trial stretch: book it
+          got[trial] += p - before;
+          took[trial] += clock64() - t0;
+        }
+        if (left == 0) {
+          if (trial == 0) {  // window tried: now the strict kind
+            trial = 1;
+            mode = 1;
+            left = TRIAL_ROUNDS;
+          } else {
+            if (trial == 1)  // both tried: elements per cycle, compared without dividing
+              mode = got[0] * took[1] >= got[1] * took[0] ? 0 : 1;
+            if (trial == 1) {
+              // the stretch grows while the same kind keeps winning (up to 16 times as long)
+              streak = mode == last_mode ? (streak < 4 ? streak + 1 : 4) : 0;
+              last_mode = mode;
+              trial = -1;
+              left = COMMIT_ROUNDS << streak;
+            } else {  // a committed stretch is over: measure again
+              trial = 0;
+              mode = 0;
+              left = TRIAL_ROUNDS;
+              got[0] = got[1] = 0;
+              took[0] = took[1] = 0;
+            }
           }
         }
       }
-    } else {  // 32 slots: a window of 32 can take every entry, the strict prefix rule stays
-      int all = 1 << 30;
-      p = strict_rounds<CELLS, TAB>(st, tab, cbase, ring, p, cnt, all);
+    } else {  // other sketch sizes: strict rounds (see WINDOW_CELLS)
+      while (p < cnt) p += round_full<CELLS, TAB>(st, tab, cbase, ring, p, cnt, lane, sink);
     }
     buf ^= 1;
   }
@@ -1429,6 +1440,7 @@ __global__ void __launch_bounds__(S_THREADS, 1) heavy_rounds_kernel(SketchArgs a
                               static_cast<size_t>(warp) * mates_words
                         : nullptr;
   for (int i = lane; i < mates_words; i += 32) mates[i] = 0u;
+
 #ifdef SPORDER_CHECKED
   if (lane == 0) {
     state[warp].ctrl = a.ctrl;
@@ -1514,6 +1526,7 @@ bool launch_cells(Context &ctx, const SketchArgs &a) {
     // round_window's duplicate detector: four bytes per row of the chunk and warp, if they fit too
     int64_t mates_words = tab_bytes;
     if (tab_bytes == 0 || ROUND_RING_BYTES + 5 * tab_bytes * S_WARPS > pad) mates_words = 0;
+
     {
       CSG_CUDA(cudaFuncSetAttribute(heavy_rounds_kernel<CELLS>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, pad));
@@ -1537,7 +1550,7 @@ bool launch_cells(Context &ctx, const SketchArgs &a) {
   // key -> slot tables for its warps when a chunk's table is small enough that the blocks of an
   // SM still fit (16 KB per block) and slot numbers fit a byte
   int light_tab = 0;
-  if constexpr (32 * CELLS <= 224) {
+  if constexpr (CELLS == WINDOW_CELLS) {
     const int64_t want = (static_cast<int64_t>(a.chunk < a.n ? a.chunk : a.n) + 15) / 16 * 16;
     if (want <= 4096) light_tab = static_cast<int>(want);
   }
@@ -1559,7 +1572,7 @@ bool launch_cells(Context &ctx, const SketchArgs &a) {
     CSG_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, 1, tab_bytes));
     return true;
   };
-  if constexpr (32 * CELLS <= 224) {
+  if constexpr (CELLS == WINDOW_CELLS) {
     if (light_tab > 0) {
       if (!launch_light(sketch_kernel<CELLS, true>, light_tab)) return false;
     } else if (!launch_light(sketch_kernel<CELLS, false>, 0)) {

@@ -62,3 +62,37 @@ def test_harness_module_imports_without_gpu_or_harness():
     assert harness.B200SpMM().name == "sporder-b200-spmm"
     r = harness.ReorderResult(row_perm=None, reorder_time_ms=1.0)
     assert r.prep_time_ms == 0.0 and r.timing_breakdown == {}
+
+
+def test_amortization_and_breakeven_formulas():
+    # bench/spmm/scripts/compute_amortization.py:63-66 and analysis/e2e.py:32-33
+    from chunkedgreedy_b200 import harness
+    assert harness.amortization_runs(40.0, 2.5, 2.0) == 80.0
+    assert harness.amortization_runs(40.0, 2.0, 2.0) == float("inf")
+    assert harness.amortization_runs(40.0, 2.0, 2.5) == float("inf")
+    assert harness.format_amortization(float("inf")) == "inf"
+    assert harness.format_amortization(80.0) == "80"
+    import importlib.util
+    if importlib.util.find_spec("torch") is None:
+        return
+    from chunkedgreedy_b200 import gcn
+    assert gcn.breakeven_epochs(60.0, 1.5, 13.0, 12.5) == 123.0
+    assert gcn.breakeven_epochs(60.0, 1.5, 12.5, 12.5) == float("inf")
+
+
+def test_library_path_can_name_another_build(monkeypatch):
+    # the checked build is loaded through SPORDER_B200_LIBRARY
+    import importlib
+    monkeypatch.setenv("SPORDER_B200_LIBRARY", "/nowhere/libsporder_b200_checked.so")
+    mod = importlib.reload(_lib)
+    try:
+        assert mod.LIB_PATH == "/nowhere/libsporder_b200_checked.so"
+        try:
+            mod.load()
+        except RuntimeError as e:
+            assert "missing" in str(e)
+        else:
+            raise AssertionError("a missing library must fail loudly")
+    finally:
+        monkeypatch.delenv("SPORDER_B200_LIBRARY")
+        importlib.reload(_lib)
