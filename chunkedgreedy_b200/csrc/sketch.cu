@@ -1067,16 +1067,19 @@ __device__ __forceinline__ int round_full(RoundState<CELLS> &st, uint8_t *tab, i
 //   * a second element with the key of an earlier one is a hit on the entry the first one
 //     left, whichever kind the first one was.
 // Only the first element of each key ("leader") with its entry among the 32 lightest can go
-// either way.  Those are walked in stream order (a handful per window, state in two 32-bit
-// masks, every lane computing the same): with P misses before element j and b skipped entries
-// below its entry's rank r, the entry is gone iff P + b > r.  The miss with i misses before it
+// either way: with P misses before element j and b skipped entries below its entry's rank r,
+// the entry is gone iff P + b > r.  Bounds on P + b settle most of them without looking at
+// the others (see "slack" below); a window where one stays undecided walks them in stream
+// order (a handful per window, state in two 32-bit masks, every lane computing the same).
+// The miss with i misses before it
 // then takes the (i+1)-th entry that no hit holds back.  The read-off is exact as long as
 // nothing put back or made heavier is light enough to be taken again inside the window; an
 // element whose new weight does not clear the heaviest entry taken ends the prefix before the
 // next miss behind it (before itself, if its weight did not grow at all).  On the heaviest
 // R-MAT rows that happens in one window of 32,000 (the row's own Dice terms dominate) to one
 // in ten (rows whose terms vary more), and a round resolves 32.0 resp. 29.3 elements where
-// round_full resolves 16.
+// round_full resolves 16.4 on the former; it costs about 1.8 times a round_full, which is why
+// rounds_row times both kinds on every row and keeps the one that resolves more per cycle.
 #ifdef CSG_WINDOW_FENCES
 #define WINDOW_FENCE(s) phase_fence(s)
 #else

@@ -57,6 +57,15 @@ __device__ __forceinline__ void load_b(const float *p, float (&out)[VEC]) {
   }
 }
 
+// base + c * wbytes as one 32 x 32 -> 64 bit multiply-add (written as a 64-bit product of
+// converted operands the compiler builds it from four multiplies and two shifts, which on
+// short rows was a third of all instructions executed)
+__device__ __forceinline__ const float *b_row(const char *base, int32_t c, int32_t wbytes) {
+  long long out;
+  asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(out) : "r"(c), "r"(wbytes), "l"(reinterpret_cast<long long>(base)));
+  return reinterpret_cast<const float *>(out);
+}
+
 struct SpmmArgs {
   int32_t n, w, nnz, unit;  // unit: cost per unit of rows (T)
   const int32_t *ptr, *ind;
@@ -128,7 +137,7 @@ __device__ __forceinline__ void fma_step(const SpmmArgs &a, int32_t p, int cnt, 
 #pragma unroll
   for (int u = 0; u < U; ++u) {
     if (u < cnt) {
-      const float *src = a.B + static_cast<size_t>(c[u]) * a.w + col0;
+      const float *src = b_row(reinterpret_cast<const char *>(a.B + col0), c[u], a.w * 4);
 #pragma unroll
       for (int pn = 0; pn < PAN; ++pn) load_b<VEC>(src + pn * G * VEC, b[u][pn]);
     } else {
@@ -160,6 +169,116 @@ __device__ __forceinline__ void store_c(float *out, const float (&acc)[VEC], boo
   }
 }
 
+// ---- units of short rows ---------------------------------------------------------------
+// A unit whose rows all have at most SHORT_MAX nonzeros (every unit of a mesh or a road
+// network) needs none of the machinery of spmm_rows_kernel's walk: the warp copies the
+// (column, value) pairs of as many rows as fit S_PAIRS into shared memory with coalesced
+// loads, its lane groups take those rows in turn, and a row is worked off in pieces of exactly
+// as many nonzeros as it has left - no predicates, no padding, one shared-memory read per
+// nonzero.  On the 9-point stencil the general walk executes some 470 instructions per four
+// rows (opcode counts of a profiler run: a third of them integer multiply-adds for
+// addresses, predicates and moves), and the kernel there is bound by instruction issue.
+constexpr int SHORT_MAX = 16;
+constexpr int S_PAIRS = 448;  // pairs staged per warp
+
+// true when every row of the staged unit is well-formed and has at most SHORT_MAX nonzeros
+__device__ __forceinline__ bool unit_is_short(const int32_t *wp, int32_t bcount, int32_t nnz, int lane) {
+  int32_t worst = 0;
+  for (int k = lane; k < bcount; k += 32) {
+    const int32_t b = wp[k], e = wp[k + 1];
+    int32_t len = e - b;
+    if (b < 0 || e < b || e > nnz) len = SHORT_MAX + 1;  // malformed: the general path deals with it
+    worst = len > worst ? len : worst;
+  }
+  return __reduce_max_sync(FULL, worst) <= SHORT_MAX;
+}
+
+// N nonzeros of a row, pairs at sp[0 .. N): gather and FMA
+template <int G, int VEC, int PAN, int N>
+__device__ __forceinline__ void short_slots(const int2 *sp, const char *bcol, int32_t wbytes,
+                                            float (&acc)[PAN][VEC]) {
+  int2 pr[N];
+  float b[N][PAN][VEC];
+#pragma unroll
+  for (int j = 0; j < N; ++j) pr[j] = sp[j];
+#pragma unroll
+  for (int j = 0; j < N; ++j) {
+    const float *src = b_row(bcol, pr[j].x, wbytes);
+#pragma unroll
+    for (int pn = 0; pn < PAN; ++pn) load_b<VEC>(src + pn * G * VEC, b[j][pn]);
+  }
+#pragma unroll
+  for (int j = 0; j < N; ++j) {
+    const float x = __int_as_float(pr[j].y);
+#pragma unroll
+    for (int pn = 0; pn < PAN; ++pn)
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) acc[pn][v] = fmaf(x, b[j][pn][v], acc[pn][v]);
+  }
+}
+
+// all rows [bfirst, bfirst + bcount) of a short unit; wp holds their row pointers, sp is the
+// warp's pair buffer
+template <int G, int VEC, int PAN>
+__device__ __forceinline__ void short_rows(const SpmmArgs &a, const int32_t *wp, int2 *sp, int32_t bfirst,
+                                           int32_t bcount, int lane) {
+  constexpr int PER_WARP = 32 / G;
+  constexpr int UC = Step<PAN>::U;
+  const int sub = lane / G, gl = lane % G;
+  const int panels = a.w / (G * VEC);
+  const int32_t wbytes = a.w * 4;
+  int32_t r0 = 0;
+  while (r0 < bcount) {
+    // rows [r0, r1): as many as the pair buffer holds (at least S_PAIRS / SHORT_MAX of them)
+    const int32_t p0 = wp[r0];
+    int32_t lo = r0 + 1, hi = bcount;
+    while (lo < hi) {
+      const int32_t mid = (lo + hi + 1) >> 1;
+      if (wp[mid] - p0 <= S_PAIRS)
+        lo = mid;
+      else
+        hi = mid - 1;
+    }
+    const int32_t r1 = lo, cnt = wp[r1] - p0;
+    __syncwarp();  // the rows before are done with the buffer
+    for (int32_t k = lane; k < cnt; k += 32)
+      sp[k] = make_int2(__ldcs(a.ind + p0 + k), __float_as_int(__ldcs(a.val + p0 + k)));
+    __syncwarp();
+    for (int32_t idx = r0 + sub; idx < r1; idx += PER_WARP) {
+      const int32_t b = wp[idx] - p0, e = wp[idx + 1] - p0;
+      float *out = a.C + static_cast<size_t>(bfirst + idx) * a.w + gl * VEC;
+      for (int pn0 = 0; pn0 < panels; pn0 += PAN) {
+        float acc[PAN][VEC];
+#pragma unroll
+        for (int pn = 0; pn < PAN; ++pn)
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) acc[pn][v] = 0.0f;
+        const char *bcol = reinterpret_cast<const char *>(a.B + pn0 * (G * VEC) + gl * VEC);
+        // pieces of UC nonzeros while more than CAP are left, then all the rest in one piece:
+        // every gather of a piece is issued before its first FMA, so a row of nine costs one
+        // trip to memory, not two
+        constexpr int CAP = UC + 1;
+        int32_t q = b;
+        for (; e - q > CAP; q += UC) short_slots<G, VEC, PAN, UC>(sp + q, bcol, wbytes, acc);
+        switch (e - q) {
+#define CSG_REST(N)                                              \
+  case N:                                                        \
+    if constexpr (N <= CAP) short_slots<G, VEC, PAN, N>(sp + q, bcol, wbytes, acc); \
+    break;
+          CSG_REST(1) CSG_REST(2) CSG_REST(3) CSG_REST(4) CSG_REST(5) CSG_REST(6) CSG_REST(7) CSG_REST(8)
+          CSG_REST(9) CSG_REST(10)
+#undef CSG_REST
+          default:
+            break;
+        }
+#pragma unroll
+        for (int pn = 0; pn < PAN; ++pn) store_c<VEC>(out + (pn0 + pn) * (G * VEC), acc[pn], false);
+      }
+    }
+    r0 = r1;
+  }
+}
+
 // First launch: all rows of up to SPLIT nonzeros.  Every lane group is persistent: it takes
 // the next row of its warp's unit as soon as its current row is finished, so the groups of
 // a warp never wait for the one with the longest row.  Rows longer than SPLIT are zeroed and
@@ -168,6 +287,7 @@ template <int G, int VEC, int PAN>
 __global__ void __launch_bounds__(M_THREADS, M_BLOCKS_PER_SM) spmm_rows_kernel(SpmmArgs a) {
   constexpr int U = Step<PAN>::U;
   __shared__ int32_t sptr[M_WARPS][BATCH_MAX + 1];
+  __shared__ int2 spair[M_WARPS][S_PAIRS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gl = lane % G;
   const unsigned below_group = (1u << (lane - gl)) - 1u;  // lanes of the groups in front of mine
@@ -176,6 +296,7 @@ __global__ void __launch_bounds__(M_THREADS, M_BLOCKS_PER_SM) spmm_rows_kernel(S
   // warp-uniform: the rows in hand [bfirst, bfirst + bcount) and how many of them are given out
   int32_t bfirst = 0, bcount = 0, bnext = 0;
   bool exhausted = false;
+  bool short_unit = false;  // the unit in hand goes to short_rows once every group is idle
   // group-uniform: the row in hand (-1: none), its extent, the walk's position and panel
   int32_t row = -1, pb = 0, p = 0, pe = 0, pn0 = 0;
   float acc[PAN][VEC];
@@ -221,10 +342,30 @@ __global__ void __launch_bounds__(M_THREADS, M_BLOCKS_PER_SM) spmm_rows_kernel(S
             __syncwarp();
             for (int k = lane; k <= bcount; k += 32) wp[k] = __ldg(a.ptr + bfirst + k);
             __syncwarp();
+            short_unit = unit_is_short(wp, bcount, a.nnz, lane);
           }
         }
       }
-      if (row < 0) {
+      bool hold = false;  // a short unit in hand: no row of it is handed out one by one
+      {
+        if (short_unit) {
+          hold = true;
+          // (groups still walking a row of the unit before finish it first)
+          if (__ballot_sync(FULL, row >= 0) == 0u) {
+            short_rows<G, VEC, PAN>(a, wp, spair[warp], bfirst, bcount, lane);
+            bnext = bcount;
+            short_unit = false;
+            // (no group holds a row here: saying so frees the walk's registers for short_rows)
+            row = -1;
+            pb = p = pe = pn0 = 0;
+#pragma unroll
+            for (int pn = 0; pn < PAN; ++pn)
+#pragma unroll
+              for (int v = 0; v < VEC; ++v) acc[pn][v] = 0.0f;
+          }
+        }
+      }
+      if (!hold && row < 0) {
         const int idx = bnext + __popc(want & below_group);
         if (idx < bcount) {
           int32_t b = wp[idx], e = wp[idx + 1];
@@ -249,8 +390,10 @@ __global__ void __launch_bounds__(M_THREADS, M_BLOCKS_PER_SM) spmm_rows_kernel(S
           }
         }
       }
-      const int given = bnext + __popc(want);
-      bnext = given < bcount ? given : bcount;
+      if (!hold) {
+        const int given = bnext + __popc(want);
+        bnext = given < bcount ? given : bcount;
+      }
       if (exhausted && __ballot_sync(FULL, row >= 0) == 0u) break;
     }
     if (row >= 0 && p < pe) {

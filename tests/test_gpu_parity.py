@@ -164,6 +164,41 @@ def test_spmm_within_1e5_of_fp64(name, w):
     assert np.all(np.abs(C - ref64) <= 1e-5 * refabs + 1e-30)
 
 
+def _rows_of_given_lengths(lengths, n_cols, seed):
+    """CSR with the given row lengths, sorted distinct columns, N(0,1) values."""
+    rng = np.random.default_rng(seed)
+    ptr = np.zeros(len(lengths) + 1, dtype=np.int32)
+    ptr[1:] = np.cumsum(lengths)
+    ind = np.empty(ptr[-1], dtype=np.int32)
+    for r, ln in enumerate(lengths):
+        ind[ptr[r]:ptr[r + 1]] = np.sort(rng.choice(n_cols, size=ln, replace=False))
+    val = rng.standard_normal(ptr[-1]).astype(np.float32)
+    return ptr, ind, val
+
+
+@pytest.mark.parametrize("w", [1, 2, 4, 8, 16, 32, 64, 96, 128, 256])
+@pytest.mark.parametrize("longest", [16, 17, 40])
+def test_spmm_on_units_of_short_rows(w, longest):
+    # rows of 0..16 nonzeros go through the kernel's path for units of short rows, every
+    # length and every remainder of a piece; with a few longer rows mixed in, units of both
+    # kinds follow one another in the same launch
+    sp = _sp()
+    n = 6000
+    rng = np.random.default_rng(7 + longest)
+    lengths = rng.integers(0, 17, size=n)
+    lengths[:40] = np.arange(40) % 17          # every length at the head of a unit
+    if longest > 16:
+        lengths[rng.choice(n, size=60, replace=False)] = longest
+    ptr, ind, val = _rows_of_given_lengths(lengths, n, 11)
+    B = np.random.default_rng(5).standard_normal((n, w)).astype(np.float32)
+    C = sp.spmm(_dev(ptr), _dev(ind), _dev(val), _dev(B)).cpu().numpy()
+    ref64, refabs = oracle.spmm_f64(ptr, ind, val, B)
+    assert np.all(np.abs(C - ref64) <= 1e-5 * refabs + 1e-30)
+    # and bit-equal run to run: no atomics on rows this short
+    C2 = sp.spmm(_dev(ptr), _dev(ind), _dev(val), _dev(B)).cpu().numpy()
+    assert np.array_equal(C, C2)
+
+
 def test_spmm_is_linear_and_permutation_consistent():
     # size-independent properties at a larger size: A(x+y) = Ax + Ay, and
     # (P A P^T)(P x) = P (A x)
