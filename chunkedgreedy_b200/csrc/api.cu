@@ -241,7 +241,7 @@ bool run_csg(Context &ctx, int32_t n, int32_t ncols, int32_t row_base, int32_t n
              const int32_t *d_ptr, const int32_t *d_ind,
              int32_t k, float ovs, int32_t chunk, int32_t *d_new_order, uint64_t *d_table,
              uint64_t table_capacity, sporder_csg_timing_t *timing, sporder_csg_stats_t *stats,
-             int32_t *k_used) {
+             int32_t *k_used, bool symmetric = false) {
   const auto wall0 = std::chrono::steady_clock::now();
   CsgParams p;
   if (!resolve_params(n, nnz, k, ovs, chunk, &p)) return false;
@@ -268,7 +268,9 @@ bool run_csg(Context &ctx, int32_t n, int32_t ncols, int32_t row_base, int32_t n
   cudaStream_t st = ctx.stream;
 
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[0], st));
-  if (!launch_transpose(ctx, n, ncols, nnz, p.chunk, d_ptr, d_ind, s)) return false;
+  // (a row block of a larger matrix does not hold the rows its columns name: no shortcut there)
+  if (!launch_transpose(ctx, n, ncols, nnz, p.chunk, d_ptr, d_ind, s, symmetric && row_base == 0 && n == ncols))
+    return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
   if (!launch_sketch(ctx, n, nnz, p, d_ptr, s, row_base, d_table != nullptr || stats != nullptr)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[2], st));
@@ -320,7 +322,8 @@ __global__ void __launch_bounds__(256) unpack_table_kernel(size_t count, const u
 // other defaults (k = min(32, max(16, 2 nnz / n)), oversampling 2), results unpacked.
 bool run_similarity_graph(Context &ctx, int32_t n, int32_t nnz, const int32_t *d_ptr, const int32_t *d_ind,
                           int32_t k, float ovs, int32_t *d_indices, float *d_weights,
-                          sporder_sim_timing_t *timing, sporder_sim_stats_t *stats, int32_t *k_used) {
+                          sporder_sim_timing_t *timing, sporder_sim_stats_t *stats, int32_t *k_used,
+                          bool symmetric = false) {
   const auto wall0 = std::chrono::steady_clock::now();
   CSG_REQUIRE(n >= 1, "n must be >= 1 (got %d)", n);
   CSG_REQUIRE(nnz >= 0, "nnz must be >= 0 (got %d)", nnz);
@@ -346,7 +349,7 @@ bool run_similarity_graph(Context &ctx, int32_t n, int32_t nnz, const int32_t *d
   if (!plan_scratch(ctx, n, nnz, p, nullptr, &s)) return false;
   cudaStream_t st = ctx.stream;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[0], st));
-  if (!launch_transpose(ctx, n, n, nnz, p.chunk, d_ptr, d_ind, s)) return false;
+  if (!launch_transpose(ctx, n, n, nnz, p.chunk, d_ptr, d_ind, s, symmetric)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
   if (!launch_sketch(ctx, n, nnz, p, d_ptr, s, 0, true)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[2], st));
@@ -385,7 +388,7 @@ bool run_similarity_graph(Context &ctx, int32_t n, int32_t nnz, const int32_t *d
 // chunks of chunk_size rows, candidates outside the chunk skipped.
 bool run_chunk_greedy(Context &ctx, int32_t n, int32_t nnz, const int32_t *d_ptr, const int32_t *d_ind,
                       int32_t k, float ovs, int32_t chunk, int32_t *d_new_order,
-                      sporder_cg_timing_t *timing, sporder_cg_stats_t *stats) {
+                      sporder_cg_timing_t *timing, sporder_cg_stats_t *stats, bool symmetric = false) {
   const auto wall0 = std::chrono::steady_clock::now();
   CsgParams pg;  // greedy: the caller's chunk; also resolves k and oversampling
   if (!resolve_params(n, nnz, k, ovs, chunk, &pg)) return false;
@@ -404,7 +407,7 @@ bool run_chunk_greedy(Context &ctx, int32_t n, int32_t nnz, const int32_t *d_ptr
   if (!plan_scratch(ctx, n, nnz, ps, nullptr, &s, pg.chunk)) return false;
   cudaStream_t st = ctx.stream;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[0], st));
-  if (!launch_transpose(ctx, n, n, nnz, ps.chunk, d_ptr, d_ind, s)) return false;
+  if (!launch_transpose(ctx, n, n, nnz, ps.chunk, d_ptr, d_ind, s, symmetric)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
   if (!launch_sketch(ctx, n, nnz, ps, d_ptr, s, 0, stats != nullptr)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[2], st));
@@ -556,7 +559,6 @@ void sporder_chunk_similarity_greedy(sporder_context_t ctx, int32_t n, int32_t n
                                      int32_t k, float oversampling, int32_t chunk_size,
                                      int32_t *d_new_order, sporder_csg_timing_t *timing,
                                      sporder_csg_stats_t *stats) {
-  (void)is_symmetric;
   csg::clear_error();
   if (!ctx) {
     csg::set_error("null context");
@@ -567,7 +569,7 @@ void sporder_chunk_similarity_greedy(sporder_context_t ctx, int32_t n, int32_t n
     return;
   }
   csg::run_csg(ctx->c, n, n, 0, nnz, d_ptr, d_ind, k, oversampling, chunk_size, d_new_order, nullptr, 0,
-               timing, stats, nullptr);
+               timing, stats, nullptr, is_symmetric);
 }
 
 int32_t sporder_csg_with_table(sporder_context_t ctx, int32_t n, int32_t nnz, const int32_t *d_ptr,
@@ -575,7 +577,6 @@ int32_t sporder_csg_with_table(sporder_context_t ctx, int32_t n, int32_t nnz, co
                                float oversampling, int32_t chunk_size, int32_t *d_new_order,
                                uint64_t *d_table, uint64_t d_table_capacity,
                                sporder_csg_timing_t *timing, sporder_csg_stats_t *stats) {
-  (void)is_symmetric;
   csg::clear_error();
   if (!ctx) {
     csg::set_error("null context");
@@ -583,7 +584,7 @@ int32_t sporder_csg_with_table(sporder_context_t ctx, int32_t n, int32_t nnz, co
   }
   int32_t k_used = -1;
   if (!csg::run_csg(ctx->c, n, n, 0, nnz, d_ptr, d_ind, k, oversampling, chunk_size, d_new_order, d_table,
-                    d_table_capacity, timing, stats, &k_used))
+                    d_table_capacity, timing, stats, &k_used, is_symmetric))
     return -1;
   return k_used;
 }
@@ -611,7 +612,6 @@ int32_t sporder_chunk_similarity_greedy_host(sporder_context_t ctx, int32_t n, i
                                              int32_t chunk_size, int32_t *h_new_order,
                                              sporder_csg_timing_t *timing,
                                              sporder_csg_stats_t *stats) {
-  (void)is_symmetric;
   csg::clear_error();
   if (!ctx || !h_ptr || !h_new_order || n < 1 || nnz < 0) {
     csg::set_error("csg_host: bad arguments");
@@ -643,7 +643,7 @@ int32_t sporder_chunk_similarity_greedy_host(sporder_context_t ctx, int32_t n, i
       CSG_CUDA(cudaMemcpyAsync(d_ind, h_ind, sizeof(int32_t) * static_cast<size_t>(nnz),
                                cudaMemcpyHostToDevice, c.stream));
     const bool ok = csg::run_csg(c, n, n, 0, nnz, d_ptr, d_ind, k, oversampling, chunk_size, d_order,
-                                 nullptr, 0, timing, stats, nullptr);
+                                 nullptr, 0, timing, stats, nullptr, is_symmetric);
     if (ok)
       CSG_CUDA(cudaMemcpyAsync(h_new_order, d_order, sizeof(int32_t) * static_cast<size_t>(n),
                                cudaMemcpyDeviceToHost, c.stream));
@@ -657,21 +657,19 @@ void sporder_chunk_greedy(sporder_context_t ctx, int32_t n, int32_t nnz, const i
                           const int32_t *d_ind, bool is_symmetric, int32_t k, float oversampling,
                           int32_t chunk_size, int32_t *d_new_order, sporder_cg_timing_t *timing,
                           sporder_cg_stats_t *stats) {
-  (void)is_symmetric;
   csg::clear_error();
   if (!ctx) {
     csg::set_error("null context");
     return;
   }
   csg::run_chunk_greedy(ctx->c, n, nnz, d_ptr, d_ind, k, oversampling, chunk_size, d_new_order, timing,
-                        stats);
+                        stats, is_symmetric);
 }
 
 int32_t sporder_similarity_graph(sporder_context_t ctx, int32_t n, int32_t nnz, const int32_t *d_ptr,
                                  const int32_t *d_ind, bool is_symmetric, int32_t k, float oversampling,
                                  int32_t *d_indices, float *d_weights, sporder_sim_timing_t *timing,
                                  sporder_sim_stats_t *stats) {
-  (void)is_symmetric;
   csg::clear_error();
   if (!ctx) {
     csg::set_error("null context");
@@ -679,7 +677,7 @@ int32_t sporder_similarity_graph(sporder_context_t ctx, int32_t n, int32_t nnz, 
   }
   int32_t k_used = -1;
   if (!csg::run_similarity_graph(ctx->c, n, nnz, d_ptr, d_ind, k, oversampling, d_indices, d_weights,
-                                 timing, stats, &k_used))
+                                 timing, stats, &k_used, is_symmetric))
     return -1;
   return k_used;
 }

@@ -132,7 +132,7 @@ constexpr int SKETCH_HEAVY_BUCKET = 17;  // rows streaming >= 65536 candidates a
 
 // stage launchers; all enqueue on ctx.stream and return false after set_error()
 bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
-                      const int32_t *d_ind, CsgScratch &s);
+                      const int32_t *d_ind, CsgScratch &s, bool symmetric = false);
 bool launch_sketch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, const int32_t *d_ptr,
                    CsgScratch &s, int32_t row_base, bool zero_table);
 bool launch_greedy(Context &ctx, int32_t n, const CsgParams &p, CsgScratch &s,

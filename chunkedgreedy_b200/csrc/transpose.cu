@@ -18,9 +18,13 @@
 // the rows with the longest streams live in exactly those - are cut into tiles and
 // sorted by the whole grid: per pass a tile histogram, a per-chunk scan and a
 // stable tile scatter, then a group search per element.
-// A caller-promised symmetric pattern needs no separate path: the transpose of a
-// symmetric pattern restricted to the chunk is what the reference reads from the
-// aliased CSR arrays (sporder/src/common/csr2csc.h:52-54).
+// A caller-promised symmetric pattern needs no sort at all: column c's rows inside a chunk
+// are the entries of ROW c that fall into the chunk's row range, already ascending, so the
+// CSR arrays themselves serve as cand[] (with the row lengths looked up) and a group is a
+// sub-range of row c found by binary search (symmetric_groups_kernel).  The reference takes
+// the same promise and reads the aliased CSR arrays as the CSC
+// (sporder/src/common/csr2csc.h:52-54); like there, a false promise gives a different
+// (still valid) permutation, never an out-of-range access.
 #include "common.cuh"
 
 namespace csg {
@@ -569,6 +573,101 @@ __global__ void __launch_bounds__(T_THREADS) heavy_emit_kernel(TransposeArgs a) 
   }
 }
 
+// ---- symmetric pattern: groups read off the CSR arrays --------------------------------
+// One thread per nonzero p = (r, c): cand[p] = (c, length of row c) - cand is the column
+// array with lengths attached - and the group of column c in r's chunk is the part of row c
+// inside [chunk start, chunk end), found with three binary searches over row c that run in
+// step (the two ends and r's own place).  Blocks take tiles of Y_TILE positions; the rows a
+// tile touches are found once per tile and their pointers staged in shared memory.
+constexpr int Y_THREADS = 256;
+constexpr int Y_TILE = 2048;
+constexpr int Y_ROWS = 2048;  // rows of a tile with pointers in shared memory (more: searched in global memory)
+
+__global__ void __launch_bounds__(Y_THREADS) symmetric_groups_kernel(TransposeArgs a) {
+  __shared__ int32_t sptr[Y_ROWS + 1];
+  __shared__ int32_t span[2];
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int32_t tiles = (a.nnz + Y_TILE - 1) / Y_TILE;
+  if (a.ptr[0] != 0 || a.ptr[a.n] != a.nnz) {  // the row search below relies on both ends
+    if (tid == 0) atomicExch(&a.ctrl[CTRL_BAD_INPUT], 1u);
+    return;
+  }
+  for (int32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const int32_t p_first = tile * Y_TILE;
+    const int32_t p_end = a.nnz - p_first < Y_TILE ? a.nnz : p_first + Y_TILE;
+    __syncthreads();
+    if (tid < 2) span[tid] = row_of(a.ptr, 0, a.n, tid ? p_end - 1 : p_first);
+    __syncthreads();
+    const int32_t r_first = span[0], r_last = span[1] < span[0] ? span[0] : span[1];
+    const int32_t nrows = r_last - r_first + 1;
+    const bool staged = nrows <= Y_ROWS;
+    if (staged)
+      for (int32_t i = tid; i <= nrows; i += Y_THREADS) sptr[i] = a.ptr[r_first + i];
+    __syncthreads();
+    for (int32_t p0 = p_first; p0 < p_end; p0 += Y_THREADS) {
+      const int32_t p = p0 + tid;
+      int32_t r = -1;
+      uint32_t add = 0;
+      if (p < p_end) {
+        r = staged ? r_first + row_of(sptr, 0, nrows, p) : row_of(a.ptr, r_first, r_last + 1, p);
+        const int32_t rb = a.ptr[r], re = a.ptr[r + 1];
+        const int32_t c = a.ind[p];
+        int32_t pc = 0, pe = 0;
+        bool ok = p >= rb && p < re && c >= 0 && c < a.n;  // (row pointers that are not ascending fail here)
+        if (ok) {
+          pc = a.ptr[c];
+          pe = a.ptr[c + 1];
+          ok = pc >= 0 && pe >= pc && pe <= a.nnz;
+        }
+        if (!ok) {
+          atomicExch(&a.ctrl[CTRL_BAD_INPUT], 1u);
+          a.cand[p] = make_int2(r, 1);
+          a.seg[p] = make_int2(p, 0);
+          a.seg_rank[p] = 0;
+        } else {
+          a.cand[p] = make_int2(c, pe - pc);
+          const int64_t q0 = static_cast<int64_t>(r / a.chunk) * a.chunk;
+          const int64_t q1 = q0 + a.chunk;
+          // first entries of row c not below the chunk start, the chunk end and r
+          int32_t lo_a = pc, hi_a = pe, lo_b = pc, hi_b = pe, lo_r = pc, hi_r = pe;
+          while (lo_a < hi_a || lo_b < hi_b || lo_r < hi_r) {
+            const int32_t ma = (lo_a + hi_a) >> 1, mb = (lo_b + hi_b) >> 1, mr = (lo_r + hi_r) >> 1;
+            const int32_t va = lo_a < hi_a ? a.ind[ma] : 0;
+            const int32_t vb = lo_b < hi_b ? a.ind[mb] : 0;
+            const int32_t vr = lo_r < hi_r ? a.ind[mr] : 0;
+            if (lo_a < hi_a) {
+              if (va < q0) lo_a = ma + 1; else hi_a = ma;
+            }
+            if (lo_b < hi_b) {
+              if (vb < q1) lo_b = mb + 1; else hi_b = mb;
+            }
+            if (lo_r < hi_r) {
+              if (vr < r) lo_r = mr + 1; else hi_r = mr;
+            }
+          }
+          // (rows that are not sorted can cross the three results: keep them ordered)
+          const int32_t first = lo_a;
+          const int32_t last = lo_b < first ? first : lo_b;
+          int32_t at = lo_r < first ? first : lo_r;
+          at = at > last ? last : at;
+          const int32_t len = last - first;
+          a.seg[p] = make_int2(first, len);
+          a.seg_rank[p] = at - first;
+          if (len >= 2) add = static_cast<uint32_t>(len - 1);
+        }
+      }
+      // the candidates each row will see: one atomic per warp where the warp sits in one row
+      const int32_t r_lead = __shfl_sync(FULL, r, 0);
+      if (__all_sync(FULL, r == r_lead || r < 0) && r_lead >= 0 && __all_sync(FULL, add < (1u << 26))) {
+        const uint32_t sum = __reduce_add_sync(FULL, add);
+        if (lane == 0 && sum) saturating_add(&a.row_work[r_lead], sum);
+      } else if (add) {
+        saturating_add(&a.row_work[r], add);
+      }
+    }
+  }
+}
+
 // rows per power-of-two bucket of row_work
 __global__ void __launch_bounds__(256) bucket_count_kernel(int32_t n, const uint32_t *row_work,
                                                            uint32_t *ctrl) {
@@ -632,7 +731,7 @@ __global__ void row_list_kernel(int32_t n, const uint32_t *__restrict__ row_work
 }  // namespace
 
 bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
-                      const int32_t *d_ind, CsgScratch &s) {
+                      const int32_t *d_ind, CsgScratch &s, bool symmetric) {
   TransposeArgs a;
   a.n = n;
   a.nnz = nnz;
@@ -662,6 +761,23 @@ bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32
   cudaStream_t st = ctx.stream;
   CSG_CUDA(cudaMemsetAsync(s.ctrl, 0, sizeof(uint32_t) * CTRL_WORDS, st));
   CSG_CUDA(cudaMemsetAsync(s.row_work, 0, sizeof(uint32_t) * static_cast<size_t>(n), st));
+  int lgrid = (n + 255) / 256;
+  if (lgrid > ctx.num_sms * 8) lgrid = ctx.num_sms * 8;
+  if (symmetric && n == ncols && nnz > 0) {
+    // the caller's promise: the pattern is its own transpose
+    int ygrid = (nnz + Y_TILE - 1) / Y_TILE;
+    if (ygrid > ctx.num_sms * 8) ygrid = ctx.num_sms * 8;
+    symmetric_groups_kernel<<<ygrid, Y_THREADS, 0, st>>>(a);
+    CSG_CUDA(cudaGetLastError());
+    bucket_count_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl);
+    CSG_CUDA(cudaGetLastError());
+    bucket_scan_kernel<<<1, 32, 0, st>>>(s.ctrl);
+    CSG_CUDA(cudaGetLastError());
+    row_list_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl, s.row_list);
+    CSG_CUDA(cudaGetLastError());
+    count_launches(4);
+    return true;
+  }
   int cgrid = (a.num_chunks + 255) / 256;
   if (cgrid > ctx.num_sms * 4) cgrid = ctx.num_sms * 4;
   classify_chunks_kernel<<<cgrid, 256, 0, st>>>(a);
@@ -684,8 +800,6 @@ bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32
   const int grid = a.num_chunks < ctx.num_sms ? a.num_chunks : ctx.num_sms;
   transpose_kernel<<<grid, T_THREADS, smem, st>>>(a);
   CSG_CUDA(cudaGetLastError());
-  int lgrid = (n + 255) / 256;
-  if (lgrid > ctx.num_sms * 8) lgrid = ctx.num_sms * 8;
   bucket_count_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl);
   CSG_CUDA(cudaGetLastError());
   bucket_scan_kernel<<<1, 32, 0, st>>>(s.ctrl);

@@ -19,10 +19,13 @@
  *     aborts: the call returns early, outputs are unspecified, and
  *     sporder_last_error() returns the message (NULL when the last call on this
  *     thread succeeded).
- *   - `is_symmetric` is accepted for compatibility and does not change the
- *     result: the library always uses the transpose of the pattern, which is what
- *     the reference reads when the promise is true
- *     (sporder/src/common/csr2csc.h:49-59).
+ *   - `is_symmetric` is the reference's promise that the pattern equals its
+ *     transpose (sporder/src/common/csr2csc.h:49-59, where the CSR arrays are then
+ *     read as the CSC).  With it the library reads the column groups straight off
+ *     the CSR arrays instead of sorting; results are the same as without it on a
+ *     symmetric pattern.  On a pattern that is not symmetric a true promise gives a
+ *     different, still valid permutation (as in the reference) and never an
+ *     out-of-range access.  Row shards (sporder_csg_shard) have no such parameter.
  */
 #ifndef SPORDER_B200_H
 #define SPORDER_B200_H
@@ -126,7 +129,7 @@ typedef struct {
  * k <= 0 -> min(32, max(16, 2 * (nnz / n))); oversampling <= 0 -> 2.0
  * (sporder/src/sporder.cpp:75-80).  The outputs must hold n * k entries for the k in
  * use; the return value is that k (the reference returns nothing), -1 on error.
- * is_symmetric does not change the result (see sporder_chunk_similarity_greedy). */
+ * is_symmetric: see sporder_chunk_similarity_greedy. */
 SPORDER_API int32_t sporder_similarity_graph(sporder_context_t ctx, int32_t n, int32_t nnz,
                                              const int32_t *d_ptr, const int32_t *d_ind,
                                              bool is_symmetric, int32_t k, float oversampling,

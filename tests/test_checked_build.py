@@ -35,6 +35,9 @@ for name in names:
     rp, ri, rv = oracle.reorder(ptr, ind, o, val, symmetric=True)
     assert np.array_equal(i2.cpu().numpy(), ri) and np.array_equal(v2.cpu().numpy(), rv), name
     assert sp.count_pillars(dp, di, 16) == oracle.count_pillars(ptr, ind, 16), name
+    if not sym:  # a false promise of symmetry: garbage candidates, but every index in bounds
+        o2 = sp.chunk_similarity_greedy(dp, di, is_symmetric=True, **params)
+        assert np.array_equal(np.sort(o2.cpu().numpy()), np.arange(ptr.size - 1)), name
 print("checked build: %%d cases clean" %% len(names))
 """
 

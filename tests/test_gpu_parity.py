@@ -164,6 +164,44 @@ def test_spmm_within_1e5_of_fp64(name, w):
     assert np.all(np.abs(C - ref64) <= 1e-5 * refabs + 1e-30)
 
 
+SYMMETRIC_CASES = ["band1000", "hubsym", "stencil48", "stencil48_natural", "road3k", "rmat11gcn",
+                   "stencil256", "rmat14gcn"]
+
+
+@pytest.mark.parametrize("name", SYMMETRIC_CASES)
+def test_symmetric_promise_reads_groups_off_the_csr_arrays_with_equal_results(name):
+    # sporder/src/common/csr2csc.h:49-59: with is_symmetric the CSR arrays stand in for the
+    # transpose.  Here that skips the chunk-local sort; table and permutation must not notice.
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build(name)
+    assert sym
+    dp, di = _dev(ptr), _dev(ind)
+    o1, t1 = sp.csg_table(dp, di, is_symmetric=True, **params)
+    o0, t0 = sp.csg_table(dp, di, is_symmetric=False, **params)
+    assert torch.equal(t1, t0) and torch.equal(o1, o0)
+    i1, w1 = sp.similarity_graph(dp, di, is_symmetric=True)
+    i0, w0 = sp.similarity_graph(dp, di, is_symmetric=False)
+    assert torch.equal(i1, i0) and torch.equal(w1, w0)
+    g1 = sp.chunk_greedy(dp, di, is_symmetric=True, chunk_size=256)
+    g0 = sp.chunk_greedy(dp, di, is_symmetric=False, chunk_size=256)
+    assert torch.equal(g1, g0)
+
+
+@pytest.mark.parametrize("name", ["rmat12", "ragged", "m96", "chunk1", "dense_ragged"])
+def test_a_false_symmetric_promise_still_gives_a_permutation(name):
+    # like the reference, the library takes the promise at its word; on a pattern that is not
+    # symmetric the candidates are then those of A + garbage, the result a valid permutation
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build(name)
+    assert not sym
+    n = ptr.size - 1
+    order = sp.chunk_similarity_greedy(_dev(ptr), _dev(ind), is_symmetric=True, **params)
+    assert np.array_equal(np.sort(order.cpu().numpy()), np.arange(n, dtype=np.int32))
+    chunk = params.get("chunk_size", 0) or 1024
+    blocks = order.cpu().numpy() // chunk
+    assert np.array_equal(blocks, np.arange(n) // chunk)  # rows never leave their chunk
+
+
 def _rows_of_given_lengths(lengths, n_cols, seed):
     """CSR with the given row lengths, sorted distinct columns, N(0,1) values."""
     rng = np.random.default_rng(seed)
