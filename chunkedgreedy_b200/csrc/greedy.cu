@@ -41,19 +41,14 @@ struct ChainStats {  // lives at ctrl[CTRL_STATS ...]
   double in_chunk_weight;  // table weights whose candidate lies in the row's own chunk
 };
 
-__global__ void __launch_bounds__(G_WARPS * 32) greedy_kernel(GreedyArgs a) {
-  extern __shared__ uint32_t g_smem[];
-  const int lane = lane_id(), warp = threadIdx.x >> 5;
-  const int32_t q = blockIdx.x * G_WARPS + warp;
-  if (q >= a.num_chunks) return;
-  const int64_t start64 = static_cast<int64_t>(q) * a.chunk;
-  const int32_t start = static_cast<int32_t>(start64);
-  const int32_t end = (start64 + a.chunk > a.n) ? a.n : static_cast<int32_t>(start64 + a.chunk);
+// The chain of chunk q = rows [start, end), run by one warp.  STAGED: the chunk's rows of the
+// table were copied to shared memory (`staged`, row-major like the table) by the block.
+template <bool STAGED>
+__device__ __forceinline__ void chain_chunk(const GreedyArgs &a, int32_t start, int32_t end, uint32_t *visited,
+                                            const uint64_t *staged) {
+  const int lane = lane_id();
   const int32_t size = end - start;
   const int32_t words = (size + 31) >> 5;
-  // two bitmaps per chunk: visited, and "row has a non-empty top-k list"
-  uint32_t *visited = a.gbitmaps ? a.gbitmaps + static_cast<size_t>(q) * 2 * a.words
-                                 : g_smem + static_cast<size_t>(warp) * 2 * a.words;
   uint32_t *nonempty = visited + a.words;
   for (int32_t w = lane; w < words; w += 32) visited[w] = 0;
   for (int32_t base = 0; base < size; base += 32) {
@@ -78,7 +73,8 @@ __global__ void __launch_bounds__(G_WARPS * 32) greedy_kernel(GreedyArgs a) {
 
     int32_t best_c = -1;
     if (nonempty[loc >> 5] & (1u << (loc & 31))) {
-      const uint64_t *row = a.table + static_cast<size_t>(cur) * a.k;
+      const uint64_t *row = STAGED ? staged + static_cast<size_t>(loc) * a.k
+                                   : a.table + static_cast<size_t>(cur) * a.k;
       uint32_t best_w = 0;  // weight bits; real weights are positive
       for (int32_t j = lane; j < a.k; j += 32) {
         const uint64_t e = row[j];
@@ -90,7 +86,7 @@ __global__ void __launch_bounds__(G_WARPS * 32) greedy_kernel(GreedyArgs a) {
         // The next row of the chain is one of these candidates, and its list is needed as
         // soon as the arg-max below is known: ask for every candidate's list now, so that the
         // one dependent load per step finds it in L1 instead of waiting on L2.
-        asm volatile("prefetch.global.L1 [%0];" ::"l"(a.table + static_cast<size_t>(cand) * a.k));
+        if (!STAGED) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.table + static_cast<size_t>(cand) * a.k));
         const uint32_t wb = entry_weight_bits(e);
         if (wb > best_w || (wb == best_w && cand < best_c)) {
           best_w = wb;
@@ -175,6 +171,40 @@ __global__ void __launch_bounds__(G_WARPS * 32) greedy_kernel(GreedyArgs a) {
     atomicAdd(&st->links, links);
     atomicAdd(&st->link_weight_sum, static_cast<double>(link_w));
   }
+}
+
+__global__ void __launch_bounds__(G_WARPS * 32) greedy_kernel(GreedyArgs a) {
+  extern __shared__ uint32_t g_smem[];
+  const int warp = threadIdx.x >> 5;
+  const int32_t q = blockIdx.x * G_WARPS + warp;
+  if (q >= a.num_chunks) return;
+  const int64_t start64 = static_cast<int64_t>(q) * a.chunk;
+  const int32_t start = static_cast<int32_t>(start64);
+  const int32_t end = (start64 + a.chunk > a.n) ? a.n : static_cast<int32_t>(start64 + a.chunk);
+  // two bitmaps per chunk: visited, and "row has a non-empty top-k list"
+  uint32_t *visited = a.gbitmaps ? a.gbitmaps + static_cast<size_t>(q) * 2 * a.words
+                                 : g_smem + static_cast<size_t>(warp) * 2 * a.words;
+  chain_chunk<false>(a, start, end, visited, nullptr);
+}
+
+// With no more chunks than SMs there are too few chains to hide one another's latency, and a
+// step is one dependent read of a table row: a block per chunk copies the chunk's rows of the
+// table into shared memory first (1024 rows x 16 entries = 128 KB), and one warp runs the
+// chain on that copy.
+constexpr int GS_THREADS = 256;
+__global__ void __launch_bounds__(GS_THREADS, 1) greedy_staged_kernel(GreedyArgs a) {
+  extern __shared__ __align__(16) uint32_t g_smem[];
+  const int32_t q = blockIdx.x;
+  const int64_t start64 = static_cast<int64_t>(q) * a.chunk;
+  const int32_t start = static_cast<int32_t>(start64);
+  const int32_t end = (start64 + a.chunk > a.n) ? a.n : static_cast<int32_t>(start64 + a.chunk);
+  uint32_t *visited = g_smem;
+  uint64_t *staged = reinterpret_cast<uint64_t *>(g_smem + ((2 * a.words + 3) & ~3));
+  const size_t entries = static_cast<size_t>(end - start) * a.k;
+  const uint64_t *src = a.table + static_cast<size_t>(start) * a.k;
+  for (size_t i = threadIdx.x; i < entries; i += GS_THREADS) staged[i] = src[i];
+  __syncthreads();
+  if (threadIdx.x < 32) chain_chunk<true>(a, start, end, visited, staged);
 }
 
 // sporder/src/common/similarity_top_k.cu:120-157
@@ -270,6 +300,17 @@ bool launch_greedy(Context &ctx, int32_t n, const CsgParams &p, CsgScratch &s,
     CSG_REQUIRE(s.gbitmaps != nullptr, "greedy: no global bitmap space was reserved");
     a.gbitmaps = s.gbitmaps;
     smem = 0;
+  }
+  // few chunks: one block per chunk with the chunk's table rows in shared memory, if they fit
+  const size_t staged_bytes = static_cast<size_t>((2 * a.words + 3) & ~3) * sizeof(uint32_t) +
+                              static_cast<size_t>(span) * p.k * sizeof(uint64_t);
+  if (a.num_chunks <= ctx.num_sms && staged_bytes + 1024 <= static_cast<size_t>(ctx.smem_optin)) {
+    CSG_CUDA(cudaFuncSetAttribute(greedy_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(staged_bytes)));
+    greedy_staged_kernel<<<a.num_chunks, GS_THREADS, staged_bytes, ctx.stream>>>(a);
+    CSG_CUDA(cudaGetLastError());
+    count_launches(1);
+    return true;
   }
   const int grid = (a.num_chunks + G_WARPS - 1) / G_WARPS;
   greedy_kernel<<<grid, G_WARPS * 32, smem, ctx.stream>>>(a);
