@@ -293,7 +293,7 @@ def run_ours(args, rank, world, local_rank):
     # a workload with a symmetric pattern is reordered with the reference's is_symmetric
     # promise when one GPU holds the whole matrix (row shards cannot use it)
     from chunkedgreedy_b200 import synth
-    sym = bool(synth.WORKLOADS[args.workload][2]) and world == 1
+    sym = bool(synth.WORKLOADS[args.workload][2]) and world == 1 and not args.no_symmetric_promise
 
     def csg_local(dp, di, **kw):
         if sym:
@@ -722,6 +722,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref-cuda", action="store_true")
     ap.add_argument("--no-spmm", action="store_true")
+    ap.add_argument("--no-symmetric-promise", action="store_true",
+                    help="reorder symmetric workloads without is_symmetric (the chunk-local sort runs)")
     ap.add_argument("--no-configs", action="store_true",
                     help="skip the short runs of the other benchmark configurations")
     ap.add_argument("--configs-budget", type=float, default=90.0,
