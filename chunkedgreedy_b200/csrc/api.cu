@@ -99,6 +99,7 @@ size_t greedy_bitmap_words(int32_t n, int32_t chunk) {
 }
 
 constexpr uint64_t STREAM_CAP_MAX = uint64_t(1) << 27;  // 2^27 elements = 1 GiB
+constexpr int32_t AHEAD_MIN_NNZ = 1 << 24;  // smaller calls do not pay for a second pipeline's launches
 
 // Stream elements the buffer of the heaviest rows gets for this call: never more than the
 // rows could stream at all (nnz * chunk span), than 1 GiB or than the caller's limit; at
@@ -118,8 +119,11 @@ uint64_t stream_capacity(const Context &ctx, size_t nnz, size_t span) {
 
 // Lays out the scratch of one csg call in the context workspace.  `transpose_only` leaves
 // out everything behind the chunk-local transpose (the pillar count needs no more).
+// With `prio` the call runs one chunk ahead of the rest (run_csg): that part gets control
+// words, work lists and tile tables of its own and a share of the stream buffer.
 bool plan_scratch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, uint64_t *user_table,
-                  CsgScratch *s, int32_t greedy_chunk = 0, bool transpose_only = false) {
+                  CsgScratch *s, int32_t greedy_chunk = 0, bool transpose_only = false,
+                  CsgScratch *prio = nullptr) {
   Arena ar;
   const size_t z = static_cast<size_t>(nnz > 0 ? nnz : 1);
   const size_t o_keyA = ar.take(4 * z), o_keyB = ar.take(4 * z);
@@ -148,6 +152,30 @@ bool plan_scratch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, uint
   const size_t pmax = transpose_only ? 1 : z / SKETCH_PART_COLS + hmax + 1;  // column slices of the heavy rows
   const size_t o_pb = ar.take(4 * (hmax + 2)), o_po = ar.take(4 * (pmax + 1));
   const size_t o_table = (user_table || transpose_only) ? 0 : ar.take(8 * static_cast<size_t>(n) * p.k);
+  // the part that runs ahead: one chunk's worth of lists, tile tables for up to all nonzeros
+  // (nothing bounds a chunk's share of them), and its share of the stream buffer - what it
+  // asked for in the context's last call plus an eighth, half the buffer on a first call
+  size_t cap_p = 0, hmax_p = 0, pmax_p = 0;
+  size_t o_p_list = 0, o_p_ctrl = 0, o_p_hc = 0, o_p_htb = 0, o_p_th = 0, o_p_db = 0, o_p_ho = 0, o_p_hst = 0,
+         o_p_pb = 0, o_p_po = 0;
+  if (prio) {
+    cap_p = ctx.stream_need_prio ? static_cast<size_t>(ctx.stream_need_prio + (ctx.stream_need_prio >> 3)) : cap / 2;
+    if (cap_p > cap - cap / 4) cap_p = cap - cap / 4;
+    if (cap_p < 1) cap_p = 1;
+    hmax_p = cap_p / (size_t(1) << (SKETCH_HEAVY_BUCKET - 1)) + 1;
+    if (hmax_p > span) hmax_p = span;
+    pmax_p = z / SKETCH_PART_COLS + hmax_p + 1;
+    o_p_list = ar.take(4 * span);
+    o_p_ctrl = ar.take(4 * CTRL_WORDS);
+    o_p_hc = ar.take(4 * 2);
+    o_p_htb = ar.take(4 * 4);
+    o_p_th = ar.take(4 * 256 * (z / 4096 + 2));
+    o_p_db = ar.take(4 * 256);
+    o_p_ho = ar.take(4 * (hmax_p + 1));
+    o_p_hst = ar.take(4 * hmax_p * 2 * (p.M / 32) * 32);
+    o_p_pb = ar.take(4 * (hmax_p + 2));
+    o_p_po = ar.take(4 * (pmax_p + 1));
+  }
   if (!ensure_workspace(ctx, ar.off)) return false;
   s->keyA = reinterpret_cast<uint32_t *>(ctx.ws + o_keyA);
   s->keyB = reinterpret_cast<uint32_t *>(ctx.ws + o_keyB);
@@ -172,17 +200,50 @@ bool plan_scratch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, uint
   s->tile_hist = reinterpret_cast<uint32_t *>(ctx.ws + o_th);
   s->digit_base = reinterpret_cast<uint32_t *>(ctx.ws + o_db);
   s->gbitmaps = bw ? reinterpret_cast<uint32_t *>(ctx.ws + o_bm) : nullptr;
+  if (prio) {
+    *prio = *s;  // the arrays indexed by nonzero, row or table entry are common to both parts
+    prio->row_list = reinterpret_cast<int32_t *>(ctx.ws + o_p_list);
+    prio->ctrl = reinterpret_cast<uint32_t *>(ctx.ws + o_p_ctrl);
+    prio->heavy_chunk = reinterpret_cast<int32_t *>(ctx.ws + o_p_hc);
+    prio->heavy_tile_base = reinterpret_cast<int32_t *>(ctx.ws + o_p_htb);
+    prio->tile_hist = reinterpret_cast<uint32_t *>(ctx.ws + o_p_th);
+    prio->digit_base = reinterpret_cast<uint32_t *>(ctx.ws + o_p_db);
+    prio->heavy_off = reinterpret_cast<uint32_t *>(ctx.ws + o_p_ho);
+    prio->heavy_state = reinterpret_cast<int32_t *>(ctx.ws + o_p_hst);
+    prio->part_base = reinterpret_cast<uint32_t *>(ctx.ws + o_p_pb);
+    prio->part_off = reinterpret_cast<uint32_t *>(ctx.ws + o_p_po);
+    // the stream buffer is cut in two: the front for the part ahead
+    prio->stream_cap = static_cast<uint32_t>(cap_p);
+    prio->heavy_max = static_cast<uint32_t>(hmax_p);
+    s->hstream = s->hstream + cap_p;
+    s->stream_cap = static_cast<uint32_t>(cap - cap_p);
+    const size_t hmax_r = (cap - cap_p) / (size_t(1) << (SKETCH_HEAVY_BUCKET - 1)) + 1;
+    if (hmax_r < s->heavy_max) s->heavy_max = static_cast<uint32_t>(hmax_r);
+  }
   return true;
 }
 
 // End of a call that ran the transpose (and possibly the sketch): the control words come
 // back with the call's one synchronisation.  Malformed input and a refused stream slice are
 // errors; the stream need of the heavy rows is remembered for the context's next call.
-bool finish_call(Context &ctx, const CsgScratch &s) {
+bool finish_call(Context &ctx, const CsgScratch &s, const CsgScratch *prio = nullptr) {
   uint32_t *h = reinterpret_cast<uint32_t *>(ctx.h_pinned);
   CSG_CUDA(cudaMemcpyAsync(h, s.ctrl, 16 * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx.stream));
+  if (prio)  // (the side stream's work has been joined into ctx.stream by now)
+    CSG_CUDA(cudaMemcpyAsync(h + 16, prio->ctrl, 16 * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx.stream));
   CSG_CUDA(cudaStreamSynchronize(ctx.stream));
   CSG_CUDA(cudaGetLastError());
+  uint64_t need_prio = 0;
+  if (prio) {  // the words of the part ahead: errors count like the others', its need is kept apart
+    const uint32_t *hp = h + 16;
+    need_prio = (static_cast<uint64_t>(hp[CTRL_HEAVY_NEED + 1]) << 32) | hp[CTRL_HEAVY_NEED];
+    if (need_prio > STREAM_CAP_MAX) need_prio = STREAM_CAP_MAX;
+    if (need_prio > ctx.stream_need_prio) ctx.stream_need_prio = need_prio;
+    h[CTRL_BAD_INPUT] |= hp[CTRL_BAD_INPUT];
+    h[CTRL_STREAM_OVERRUN] |= hp[CTRL_STREAM_OVERRUN];
+    if (h[CTRL_CHECK] == 0 && hp[CTRL_CHECK] != 0)
+      for (int i = 0; i < 3; ++i) h[CTRL_CHECK + i] = hp[CTRL_CHECK + i];
+  }
   CSG_REQUIRE(h[CTRL_BAD_INPUT] == 0,
               "malformed CSR: row pointers must be non-decreasing inside [0, nnz] (results unspecified)");
   if (h[CTRL_CHECK] != 0) {  // only a build with -DSPORDER_CHECKED writes this word
@@ -198,7 +259,7 @@ bool finish_call(Context &ctx, const CsgScratch &s) {
   }
   CSG_REQUIRE(h[CTRL_STREAM_OVERRUN] == 0,
               "internal: a heavy row's stream slice did not fit its place in the stream buffer");
-  uint64_t need = (static_cast<uint64_t>(h[CTRL_HEAVY_NEED + 1]) << 32) | h[CTRL_HEAVY_NEED];
+  uint64_t need = ((static_cast<uint64_t>(h[CTRL_HEAVY_NEED + 1]) << 32) | h[CTRL_HEAVY_NEED]) + need_prio;
   if (need > STREAM_CAP_MAX) need = STREAM_CAP_MAX;
   if (need > ctx.stream_need_seen) ctx.stream_need_seen = need;
 #ifdef CSG_ROUND_PROFILE
@@ -263,16 +324,43 @@ bool run_csg(Context &ctx, int32_t n, int32_t ncols, int32_t row_base, int32_t n
               static_cast<unsigned long long>(table_capacity),
               static_cast<unsigned long long>(static_cast<uint64_t>(n) * p.k));
   CSG_CUDA(cudaSetDevice(ctx.device));
-  CsgScratch s;
-  if (!plan_scratch(ctx, n, nnz, p, d_table, &s)) return false;
+  // (a row block of a larger matrix does not hold the rows its columns name: no shortcut there)
+  const bool sym_path = symmetric && row_base == 0 && n == ncols;
+  // Large calls run one chunk ahead.  On power-law inputs the rows with the longest candidate
+  // streams - the dependent chains that decide how long the call takes - sit in the chunk
+  // with the most nonzeros, and all their chains need is that chunk's own transposition.  So
+  // that chunk is transposed first, on a second stream, and its heavy rows' chains start
+  // there while the context's stream transposes everything else; the two meet before the
+  // greedy stage.  Results do not depend on the split (the same kernels on the same rows).
+  const int64_t chunks = (static_cast<int64_t>(n) + p.chunk - 1) / p.chunk;
+  const bool ahead = !sym_path && ctx.side_stream != nullptr && nnz >= AHEAD_MIN_NNZ && chunks >= 64 &&
+                     p.chunk <= 4096 && std::getenv("SPORDER_B200_NO_AHEAD") == nullptr;
+  CsgScratch s, sp;
+  if (!plan_scratch(ctx, n, nnz, p, d_table, &s, 0, false, ahead ? &sp : nullptr)) return false;
   cudaStream_t st = ctx.stream;
+  const bool zero_table = d_table != nullptr || stats != nullptr;
 
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[0], st));
-  // (a row block of a larger matrix does not hold the rows its columns name: no shortcut there)
-  if (!launch_transpose(ctx, n, ncols, nnz, p.chunk, d_ptr, d_ind, s, symmetric && row_base == 0 && n == ncols))
-    return false;
-  if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
-  if (!launch_sketch(ctx, n, nnz, p, d_ptr, s, row_base, d_table != nullptr || stats != nullptr)) return false;
+  if (!ahead) {
+    if (!launch_transpose(ctx, n, ncols, nnz, p.chunk, d_ptr, d_ind, s, sym_path)) return false;
+    if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
+    if (!launch_sketch(ctx, n, nnz, p, d_ptr, s, row_base, zero_table)) return false;
+  } else {
+    if (zero_table)
+      CSG_CUDA(cudaMemsetAsync(s.table, 0, sizeof(uint64_t) * static_cast<size_t>(n) * p.k, st));
+    if (!launch_priority_pick(ctx, n, nnz, p.chunk, d_ptr, s, sp)) return false;
+    CSG_CUDA(cudaEventRecord(ctx.ev[5], st));
+    CSG_CUDA(cudaStreamWaitEvent(ctx.side_stream, ctx.ev[5], 0));
+    // the chunk ahead: queued first, so that the host's launches of the rest do not delay it
+    if (!launch_transpose(ctx, n, ncols, nnz, p.chunk, d_ptr, d_ind, sp, false, PHASE_PRIO, s.ctrl)) return false;
+    if (!launch_sketch(ctx, n, nnz, p, d_ptr, sp, row_base, false, PHASE_PRIO)) return false;
+    CSG_CUDA(cudaEventRecord(ctx.ev[7], ctx.side_stream));
+    if (!launch_transpose(ctx, n, ncols, nnz, p.chunk, d_ptr, d_ind, s, false, PHASE_REST)) return false;
+    if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
+    CSG_CUDA(cudaStreamWaitEvent(st, ctx.ev[8], 0));
+    if (!launch_sketch(ctx, n, nnz, p, d_ptr, s, row_base, false, PHASE_REST)) return false;
+    CSG_CUDA(cudaStreamWaitEvent(st, ctx.ev[7], 0));
+  }
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[2], st));
   if (stats && !launch_table_stats(ctx, n, p.k, s.table, s.ctrl)) return false;
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[3], st));
@@ -283,7 +371,7 @@ bool run_csg(Context &ctx, int32_t n, int32_t ncols, int32_t row_base, int32_t n
   ChainStatsHost hs;
   if (stats)
     CSG_CUDA(cudaMemcpyAsync(&hs, s.ctrl + CTRL_STATS, sizeof(hs), cudaMemcpyDeviceToHost, st));
-  if (!finish_call(ctx, s)) return false;
+  if (!finish_call(ctx, s, ahead ? &sp : nullptr)) return false;
   if (stats) {  // sporder/src/csg/stats_collector.cu:53-62
     stats->avg_degree = static_cast<double>(hs.total_degree) / n;
     stats->avg_edge_weight =
@@ -512,6 +600,13 @@ sporder_context_t sporder_context_create(void) {
   if ((e = cudaStreamCreateWithFlags(&c.own_stream, cudaStreamNonBlocking)) != cudaSuccess)
     return fail(e, "cudaStreamCreate");
   c.stream = c.own_stream;
+  {  // the stream of the part of a large call that runs ahead: highest priority, so that its
+     // small kernels are placed before the blocks of the grids on the main stream
+    int least = 0, greatest = 0;
+    if ((e = cudaDeviceGetStreamPriorityRange(&least, &greatest)) != cudaSuccess) return fail(e, "stream priorities");
+    if ((e = cudaStreamCreateWithPriority(&c.side_stream, cudaStreamNonBlocking, greatest)) != cudaSuccess)
+      return fail(e, "cudaStreamCreateWithPriority");
+  }
   cudaDeviceGetAttribute(&c.num_sms, cudaDevAttrMultiProcessorCount, c.device);
   cudaDeviceGetAttribute(&c.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, c.device);
   for (auto &ev : c.ev)
@@ -526,12 +621,14 @@ void sporder_context_destroy(sporder_context_t h) {
   csg::Context &c = h->c;
   cudaSetDevice(c.device);
   cudaStreamSynchronize(c.stream);
+  if (c.side_stream) cudaStreamSynchronize(c.side_stream);
   if (c.ws) cudaFree(c.ws);
   if (c.stage) cudaFree(c.stage);
   for (auto &ev : c.ev)
     if (ev) cudaEventDestroy(ev);
   if (c.h_pinned) cudaFreeHost(c.h_pinned);
   if (c.own_stream) cudaStreamDestroy(c.own_stream);
+  if (c.side_stream) cudaStreamDestroy(c.side_stream);
   delete h;
 }
 

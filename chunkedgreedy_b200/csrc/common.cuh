@@ -48,7 +48,7 @@ struct Context {
   int smem_optin = 0;  // max dynamic shared memory per block (opt-in)
   char *ws = nullptr;  // device workspace
   size_t ws_bytes = 0;
-  cudaEvent_t ev[8] = {};
+  cudaEvent_t ev[10] = {};  // [0..4] stage times; [5..8] fork, joins and order of a call that runs one chunk ahead
   int *h_pinned = nullptr;  // small pinned host buffer for counters (64 ints)
   char *stage = nullptr;    // device copies of host inputs (host-buffer entry point), kept between calls
   size_t stage_bytes = 0;
@@ -58,6 +58,10 @@ struct Context {
   // context plans that much (rows that do not fit are still computed, by the slower kernel of
   // the light rows, so results never depend on the size).
   uint64_t stream_need_seen = 0;   // largest need any call of this context reported
+  uint64_t stream_need_prio = 0;   // ... and the share of it that the rows running ahead asked for
+  // Second stream (higher priority) for the part of a large call that runs ahead of the rest:
+  // the transposition and the chains of the chunk that holds the most nonzeros (see run_csg).
+  cudaStream_t side_stream = nullptr;
   uint64_t stream_limit = 0;       // caller's upper bound (sporder_context_set_stream_limit), 0 = none
 };
 
@@ -120,6 +124,7 @@ enum {
   CTRL_STREAM_OVERRUN = 12,  // set by heavy_expand_kernel when a slice would pass the stream buffer
   CTRL_CHECK = 13,         // checked build: site of the first index out of bounds, then the index (64-bit)
   CTRL_BUCKET_COUNT = 16,  // 33 entries
+  CTRL_PRIO = 50,          // chunk whose heavy rows run ahead of the rest (PRIO_NONE: no such chunk)
   CTRL_BUCKET_BASE = 56,   // 33 entries
   CTRL_BUCKET_FILL = 96,   // 33 entries
   CTRL_STATS = 136,        // see greedy.cu (8-byte aligned)
@@ -127,14 +132,24 @@ enum {
   CTRL_WORDS = 200
 };
 
+constexpr uint32_t PRIO_NONE = 0xFFFFFFFFu;
+// phases of a call that runs one chunk ahead: everything (no such split), the chunk ahead, the rest
+enum CallPhase { PHASE_ALL = 0, PHASE_PRIO = 1, PHASE_REST = 2 };
+// SMs the chains of the chunk ahead may hold (the other chains get the remaining ones)
+inline int prio_chain_blocks(int num_sms) { return num_sms / 4 > 0 ? num_sms / 4 : 1; }
+
 constexpr int SKETCH_PART_COLS = 128;   // columns of a heavy row whose stream one warp writes out
 constexpr int SKETCH_HEAVY_BUCKET = 17;  // rows streaming >= 65536 candidates are "heavy"
 
 // stage launchers; all enqueue on ctx.stream and return false after set_error()
 bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
-                      const int32_t *d_ind, CsgScratch &s, bool symmetric = false);
+                      const int32_t *d_ind, CsgScratch &s, bool symmetric = false, int phase = PHASE_ALL,
+                      uint32_t *ctrl_main = nullptr);
+// start of a call that runs one chunk ahead: clears the counters of both parts and names the chunk
+bool launch_priority_pick(Context &ctx, int32_t n, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
+                          CsgScratch &s, CsgScratch &prio);
 bool launch_sketch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, const int32_t *d_ptr,
-                   CsgScratch &s, int32_t row_base, bool zero_table);
+                   CsgScratch &s, int32_t row_base, bool zero_table, int phase = PHASE_ALL);
 bool launch_greedy(Context &ctx, int32_t n, const CsgParams &p, CsgScratch &s,
                    int32_t *d_new_order, bool with_stats, int32_t row_base);
 bool launch_pillars_search(Context &ctx, int32_t n, int32_t nnz, int32_t height, const int32_t *d_ptr,

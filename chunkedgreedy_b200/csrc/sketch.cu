@@ -1507,15 +1507,27 @@ __global__ void __launch_bounds__(S_THREADS) heavy_topk_kernel(SketchArgs a) {
 }
 
 template <int CELLS>
-bool launch_cells(Context &ctx, const SketchArgs &a) {
-  heavy_offsets_kernel<<<1, 1024, 0, ctx.stream>>>(a);
+bool launch_cells(Context &ctx, const SketchArgs &a, int phase) {
+  // A call that runs one chunk ahead has two of these sequences in flight: the chunk ahead on
+  // the side stream with a quarter of the SMs for its chains, the rest on the context's stream
+  // with the other three quarters (a chain block takes a whole SM, and the kernel of the other
+  // rows starts only when every chain block has one).
+  cudaStream_t st = phase == PHASE_PRIO ? ctx.side_stream : ctx.stream;
+  const int chain_blocks = phase == PHASE_PRIO   ? prio_chain_blocks(ctx.num_sms)
+                           : phase == PHASE_REST ? ctx.num_sms - prio_chain_blocks(ctx.num_sms)
+                                                 : ctx.num_sms;
+  heavy_offsets_kernel<<<1, 1024, 0, st>>>(a);
   CSG_CUDA(cudaGetLastError());
-  heavy_part_count_kernel<<<ctx.num_sms * 4, 256, 0, ctx.stream>>>(a);
+  heavy_part_count_kernel<<<ctx.num_sms * 4, 256, 0, st>>>(a);
   CSG_CUDA(cudaGetLastError());
-  heavy_part_scan_kernel<<<1, 1024, 0, ctx.stream>>>(a);
+  heavy_part_scan_kernel<<<1, 1024, 0, st>>>(a);
   CSG_CUDA(cudaGetLastError());
-  heavy_expand_kernel<<<ctx.num_sms * 8, S_THREADS, 0, ctx.stream>>>(a);
+  heavy_expand_kernel<<<ctx.num_sms * 8, S_THREADS, 0, st>>>(a);
   CSG_CUDA(cudaGetLastError());
+  // (the rest of the call starts its own chains only behind this point: by then the chains
+  // ahead, next in their stream, hold their SMs, and the kernel of the other rows cannot
+  // settle on them first)
+  if (phase == PHASE_PRIO) CSG_CUDA(cudaEventRecord(ctx.ev[8], st));
   // The chain kernel asks for all the shared memory of an SM, so that it runs one block
   // per SM.  Sketches of up to ROUND_CELLS cells per lane are resolved in rounds, with key
   // tables for a block's four warps (one byte per row of a chunk each) when they fit in there.
@@ -1533,8 +1545,8 @@ bool launch_cells(Context &ctx, const SketchArgs &a) {
     {
       CSG_CUDA(cudaFuncSetAttribute(heavy_rounds_kernel<CELLS>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, pad));
-      heavy_rounds_kernel<CELLS><<<ctx.num_sms, S_THREADS, pad, ctx.stream>>>(a, static_cast<int>(tab_bytes),
-                                                                            static_cast<int>(mates_words));
+      heavy_rounds_kernel<CELLS><<<chain_blocks, S_THREADS, pad, st>>>(a, static_cast<int>(tab_bytes),
+                                                                     static_cast<int>(mates_words));
       CSG_CUDA(cudaGetLastError());
       in_rounds = true;
     }
@@ -1543,7 +1555,7 @@ bool launch_cells(Context &ctx, const SketchArgs &a) {
     const int pad = ctx.smem_optin - 1024 - 2 * S_WARPS * S_RING * 4;
     CSG_CUDA(cudaFuncSetAttribute(heavy_consume_kernel<CELLS>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, pad));
-    heavy_consume_kernel<CELLS><<<ctx.num_sms, S_THREADS, pad, ctx.stream>>>(a);
+    heavy_consume_kernel<CELLS><<<chain_blocks, S_THREADS, pad, st>>>(a);
     CSG_CUDA(cudaGetLastError());
   }
   // The other rows run beside the heavy chains: their kernel follows in the same stream
@@ -1566,13 +1578,16 @@ bool launch_cells(Context &ctx, const SketchArgs &a) {
     cfg.gridDim = dim3(ctx.num_sms * per_sm);
     cfg.blockDim = dim3(S_THREADS);
     cfg.dynamicSmemBytes = dyn;
-    cfg.stream = ctx.stream;
+    cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    CSG_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, 1, tab_bytes));
+    // The chunk ahead has listed only its heavy rows: its kernel of the other rows has work
+    // only if some of them did not fit the stream buffer.  It runs behind the chains in plain
+    // stream order, where its idle blocks would otherwise sit on the SMs until the chains end.
+    cfg.numAttrs = phase == PHASE_PRIO ? 0 : 1;
+    CSG_CUDA(cudaLaunchKernelEx(&cfg, kernel, a, phase == PHASE_PRIO ? 0 : 1, tab_bytes));
     return true;
   };
   if constexpr (CELLS == WINDOW_CELLS) {
@@ -1584,7 +1599,7 @@ bool launch_cells(Context &ctx, const SketchArgs &a) {
   } else if (!launch_light(sketch_kernel<CELLS, false>, 0)) {
     return false;
   }
-  heavy_topk_kernel<CELLS><<<ctx.num_sms, S_THREADS, 0, ctx.stream>>>(a);
+  heavy_topk_kernel<CELLS><<<ctx.num_sms, S_THREADS, 0, st>>>(a);
   CSG_CUDA(cudaGetLastError());
   count_launches(7);
   return true;
@@ -1593,7 +1608,7 @@ bool launch_cells(Context &ctx, const SketchArgs &a) {
 }  // namespace
 
 bool launch_sketch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, const int32_t *d_ptr,
-                   CsgScratch &s, int32_t row_base, bool zero_table) {
+                   CsgScratch &s, int32_t row_base, bool zero_table, int phase) {
   SketchArgs a;
   a.n = n;
   a.nnz = nnz;
@@ -1623,7 +1638,7 @@ bool launch_sketch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, con
   switch (p.M / 32) {
 #define CSG_CASE(C) \
   case C:           \
-    return launch_cells<C>(ctx, a);
+    return launch_cells<C>(ctx, a, phase);
     CSG_CASE(1) CSG_CASE(2) CSG_CASE(3) CSG_CASE(4) CSG_CASE(5) CSG_CASE(6) CSG_CASE(7) CSG_CASE(8)
     CSG_CASE(9) CSG_CASE(10) CSG_CASE(11) CSG_CASE(12) CSG_CASE(13) CSG_CASE(14) CSG_CASE(15)
     CSG_CASE(16)

@@ -51,6 +51,10 @@ struct TransposeArgs {
   int32_t *heavy_tile_base;  // first tile of each heavy chunk, plus the total
   uint32_t *tile_hist;       // [tile][256] digit counts, then offsets
   uint32_t *digit_base;      // [heavy chunk][256]
+  // a call that runs one chunk ahead: the control words that name the chunk, and whether this
+  // pass leaves that chunk out (nullptr / false otherwise)
+  const uint32_t *ctrl_main;
+  bool skip_prio;
 };
 
 struct ChunkSpan {
@@ -307,7 +311,75 @@ __global__ void classify_chunks_kernel(TransposeArgs a) {
   for (int32_t q = blockIdx.x * blockDim.x + threadIdx.x; q < a.num_chunks;
        q += gridDim.x * blockDim.x) {
     const ChunkSpan c = chunk_span(a, q);
+    if (a.skip_prio && static_cast<uint32_t>(q) == a.ctrl_main[CTRL_PRIO]) continue;
     if (c.L > T_LS) a.heavy_chunk[atomicAdd(&a.ctrl[CTRL_HEAVY_COUNT], 1u)] = q;
+  }
+}
+
+// The chunk that runs ahead of the rest: the one with the most nonzeros, if it is a heavy
+// chunk of at least PRIO_MIN_NNZ nonzeros (a row that streams 65,536 candidates or more
+// needs a chunk about that big).  It becomes the only entry of `ap`'s list of heavy chunks.
+constexpr int32_t PRIO_MIN_NNZ = 1 << 17;
+__global__ void __launch_bounds__(1024) pick_priority_kernel(TransposeArgs a, TransposeArgs ap) {
+  __shared__ unsigned long long best[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned long long mine = 0;  // (nonzeros << 32) | ~chunk: the first of equally heavy chunks wins
+  for (int32_t q = threadIdx.x; q < a.num_chunks; q += blockDim.x) {
+    const ChunkSpan c = chunk_span(a, q);
+    const unsigned long long v = (static_cast<unsigned long long>(c.L) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(q));
+    mine = v > mine ? v : mine;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const unsigned long long t = __shfl_down_sync(FULL, mine, off);
+    mine = t > mine ? t : mine;
+  }
+  if (lane == 0) best[warp] = mine;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 32; ++w) mine = best[w] > mine ? best[w] : mine;
+    const int32_t L = static_cast<int32_t>(mine >> 32);
+    const uint32_t q = 0xFFFFFFFFu - static_cast<uint32_t>(mine);
+    const bool on = L > T_LS && L >= PRIO_MIN_NNZ;
+    a.ctrl[CTRL_PRIO] = on ? q : PRIO_NONE;
+    ap.ctrl[CTRL_PRIO] = on ? q : PRIO_NONE;
+    ap.ctrl[CTRL_HEAVY_COUNT] = on ? 1u : 0u;
+    ap.heavy_chunk[0] = on ? static_cast<int32_t>(q) : 0;
+  }
+}
+
+// Work list of the chunk ahead: its rows that stream 65,536 candidates or more, heaviest
+// bucket first (the other rows of the chunk go with everybody else's).  One block.
+__global__ void __launch_bounds__(1024) priority_rows_kernel(TransposeArgs ap, int32_t *row_list) {
+  __shared__ uint32_t count;
+  __shared__ unsigned long long need;
+  if (threadIdx.x == 0) {
+    count = 0;
+    need = 0;
+  }
+  __syncthreads();
+  const uint32_t prio = ap.ctrl[CTRL_PRIO];
+  if (prio != PRIO_NONE) {
+    const int64_t start = static_cast<int64_t>(prio) * ap.chunk;
+    const int64_t end = start + ap.chunk < ap.n ? start + ap.chunk : ap.n;
+    for (int b = 32; b >= SKETCH_HEAVY_BUCKET; --b) {
+      for (int64_t r = start + threadIdx.x; r < end; r += blockDim.x) {
+        const uint32_t t = ap.row_work[r];
+        if (t && 32 - __clz(t) == b) {
+          row_list[atomicAdd(&count, 1u)] = static_cast<int32_t>(r);
+          atomicAdd(&need, static_cast<unsigned long long>(t));
+        }
+      }
+      __syncthreads();
+    }
+  }
+  if (threadIdx.x == 0) {
+    ap.ctrl[CTRL_ROWS_LISTED] = count;
+    ap.ctrl[CTRL_HEAVY_ROWS] = count;
+    ap.ctrl[CTRL_ROW_TICKET] = count;
+    ap.ctrl[CTRL_HEAVY_TICKET] = 0;
+    ap.ctrl[CTRL_HEAVY_TICKET + 1] = 0;
+    *reinterpret_cast<unsigned long long *>(ap.ctrl + CTRL_HEAVY_NEED) = need;
   }
 }
 
@@ -669,15 +741,23 @@ __global__ void __launch_bounds__(Y_THREADS) symmetric_groups_kernel(TransposeAr
 }
 
 // rows per power-of-two bucket of row_work
+// rows of the chunk that runs ahead which that part of the call takes itself
+__device__ __forceinline__ bool taken_ahead(uint32_t prio, int32_t chunk, int32_t r, uint32_t work) {
+  return prio != PRIO_NONE && work >= (1u << (SKETCH_HEAVY_BUCKET - 1)) &&
+         static_cast<uint32_t>(r / chunk) == prio;
+}
+
 __global__ void __launch_bounds__(256) bucket_count_kernel(int32_t n, const uint32_t *row_work,
-                                                           uint32_t *ctrl) {
+                                                           uint32_t *ctrl, int32_t chunk, bool skip_prio) {
   __shared__ uint32_t bucket[33];
   __shared__ unsigned long long need;
   if (threadIdx.x < 33) bucket[threadIdx.x] = 0;
   if (threadIdx.x == 0) need = 0;
   __syncthreads();
+  const uint32_t prio = skip_prio ? ctrl[CTRL_PRIO] : PRIO_NONE;
   for (int32_t r = blockIdx.x * blockDim.x + threadIdx.x; r < n; r += gridDim.x * blockDim.x) {
-    const uint32_t t = __ldcg(row_work + r);
+    uint32_t t = __ldcg(row_work + r);
+    if (taken_ahead(prio, chunk, r, t)) t = 0;
     if (t) atomicAdd(&bucket[32 - __clz(t)], 1u);
     // stream elements of the rows heavy enough for a materialised stream: what the stream
     // buffer would have to hold for all of them (the host sizes the next call's buffer by it)
@@ -710,12 +790,14 @@ __global__ void bucket_scan_kernel(uint32_t *ctrl) {
 }
 
 __global__ void row_list_kernel(int32_t n, const uint32_t *__restrict__ row_work, uint32_t *ctrl,
-                                int32_t *__restrict__ row_list) {
+                                int32_t *__restrict__ row_list, int32_t chunk, bool skip_prio) {
   const int lane = threadIdx.x & 31;
   const int32_t total = gridDim.x * blockDim.x;
+  const uint32_t prio = skip_prio ? ctrl[CTRL_PRIO] : PRIO_NONE;
   for (int32_t base = blockIdx.x * blockDim.x; base < n; base += total) {
     const int32_t r = base + threadIdx.x;
-    const uint32_t t = r < n ? row_work[r] : 0u;
+    uint32_t t = r < n ? row_work[r] : 0u;
+    if (r < n && taken_ahead(prio, chunk, r, t)) t = 0;
     const uint32_t bkt = t ? (32 - __clz(t)) : 0u;
     const unsigned peers = __match_any_sync(FULL, bkt);
     if (bkt) {
@@ -730,8 +812,9 @@ __global__ void row_list_kernel(int32_t n, const uint32_t *__restrict__ row_work
 
 }  // namespace
 
-bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
-                      const int32_t *d_ind, CsgScratch &s, bool symmetric) {
+namespace {
+TransposeArgs transpose_args(int32_t n, int32_t ncols, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
+                             const int32_t *d_ind, const CsgScratch &s) {
   TransposeArgs a;
   a.n = n;
   a.nnz = nnz;
@@ -755,38 +838,73 @@ bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32
   a.heavy_tile_base = s.heavy_tile_base;
   a.tile_hist = s.tile_hist;
   a.digit_base = s.digit_base;
+  a.ctrl_main = nullptr;
+  a.skip_prio = false;
+  return a;
+}
+}  // namespace
+
+bool launch_priority_pick(Context &ctx, int32_t n, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
+                          CsgScratch &s, CsgScratch &prio) {
+  const TransposeArgs a = transpose_args(n, n, nnz, chunk, d_ptr, nullptr, s);
+  const TransposeArgs ap = transpose_args(n, n, nnz, chunk, d_ptr, nullptr, prio);
+  cudaStream_t st = ctx.stream;
+  CSG_CUDA(cudaMemsetAsync(s.ctrl, 0, sizeof(uint32_t) * CTRL_WORDS, st));
+  CSG_CUDA(cudaMemsetAsync(prio.ctrl, 0, sizeof(uint32_t) * CTRL_WORDS, st));
+  CSG_CUDA(cudaMemsetAsync(s.row_work, 0, sizeof(uint32_t) * static_cast<size_t>(n), st));
+  pick_priority_kernel<<<1, 1024, 0, st>>>(a, ap);
+  CSG_CUDA(cudaGetLastError());
+  count_launches(1);
+  return true;
+}
+
+// phase PHASE_ALL: the whole transposition on the context's stream.  PHASE_PRIO (on the side
+// stream, `s` = the scratch of the part that runs ahead): the one chunk launch_priority_pick
+// named, then that chunk's list of heavy rows; ctx.ev[6] marks the end of its transposition.
+// PHASE_REST (context's stream): every other chunk, then - once ev[6] has passed, because the
+// lists read the work counters of all rows - the lists of everything the part ahead left.
+bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
+                      const int32_t *d_ind, CsgScratch &s, bool symmetric, int phase, uint32_t *ctrl_main) {
+  TransposeArgs a = transpose_args(n, ncols, nnz, chunk, d_ptr, d_ind, s);
+  a.ctrl_main = ctrl_main ? ctrl_main : s.ctrl;
+  a.skip_prio = phase == PHASE_REST;
   const size_t smem = sizeof(Shared);
   CSG_CUDA(cudaFuncSetAttribute(transpose_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(smem)));
-  cudaStream_t st = ctx.stream;
-  CSG_CUDA(cudaMemsetAsync(s.ctrl, 0, sizeof(uint32_t) * CTRL_WORDS, st));
-  CSG_CUDA(cudaMemsetAsync(s.row_work, 0, sizeof(uint32_t) * static_cast<size_t>(n), st));
+  cudaStream_t st = phase == PHASE_PRIO ? ctx.side_stream : ctx.stream;
+  if (phase == PHASE_ALL) {
+    CSG_CUDA(cudaMemsetAsync(s.ctrl, 0, sizeof(uint32_t) * CTRL_WORDS, st));
+    CSG_CUDA(cudaMemsetAsync(s.row_work, 0, sizeof(uint32_t) * static_cast<size_t>(n), st));
+  }
   int lgrid = (n + 255) / 256;
   if (lgrid > ctx.num_sms * 8) lgrid = ctx.num_sms * 8;
-  if (symmetric && n == ncols && nnz > 0) {
+  if (phase == PHASE_ALL && symmetric && n == ncols && nnz > 0) {
     // the caller's promise: the pattern is its own transpose
     int ygrid = (nnz + Y_TILE - 1) / Y_TILE;
     if (ygrid > ctx.num_sms * 8) ygrid = ctx.num_sms * 8;
     symmetric_groups_kernel<<<ygrid, Y_THREADS, 0, st>>>(a);
     CSG_CUDA(cudaGetLastError());
-    bucket_count_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl);
+    bucket_count_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl, chunk, false);
     CSG_CUDA(cudaGetLastError());
     bucket_scan_kernel<<<1, 32, 0, st>>>(s.ctrl);
     CSG_CUDA(cudaGetLastError());
-    row_list_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl, s.row_list);
+    row_list_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl, s.row_list, chunk, false);
     CSG_CUDA(cudaGetLastError());
     count_launches(4);
     return true;
   }
-  int cgrid = (a.num_chunks + 255) / 256;
-  if (cgrid > ctx.num_sms * 4) cgrid = ctx.num_sms * 4;
-  classify_chunks_kernel<<<cgrid, 256, 0, st>>>(a);
-  CSG_CUDA(cudaGetLastError());
+  if (phase != PHASE_PRIO) {  // (the part ahead got its one heavy chunk from launch_priority_pick)
+    int cgrid = (a.num_chunks + 255) / 256;
+    if (cgrid > ctx.num_sms * 4) cgrid = ctx.num_sms * 4;
+    classify_chunks_kernel<<<cgrid, 256, 0, st>>>(a);
+    CSG_CUDA(cudaGetLastError());
+  }
   heavy_tiles_kernel<<<1, 1024, 0, st>>>(a);
   CSG_CUDA(cudaGetLastError());
   // heavy chunks first: the rows with the longest streams live in them
   const int hgrid = ctx.num_sms * 2;
   int sgrid = a.num_chunks < ctx.num_sms ? a.num_chunks : ctx.num_sms;
+  if (phase == PHASE_PRIO) sgrid = 1;
   for (int ps = 0; ps < a.passes; ++ps) {
     heavy_hist_kernel<<<hgrid, T_THREADS, 0, st>>>(a, ps);
     CSG_CUDA(cudaGetLastError());
@@ -797,14 +915,22 @@ bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32
   }
   heavy_emit_kernel<<<hgrid * 2, T_THREADS, 0, st>>>(a);
   CSG_CUDA(cudaGetLastError());
+  if (phase == PHASE_PRIO) {
+    CSG_CUDA(cudaEventRecord(ctx.ev[6], st));
+    priority_rows_kernel<<<1, 1024, 0, st>>>(a, s.row_list);
+    CSG_CUDA(cudaGetLastError());
+    count_launches(3 + 3 * a.passes);
+    return true;
+  }
   const int grid = a.num_chunks < ctx.num_sms ? a.num_chunks : ctx.num_sms;
   transpose_kernel<<<grid, T_THREADS, smem, st>>>(a);
   CSG_CUDA(cudaGetLastError());
-  bucket_count_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl);
+  if (phase == PHASE_REST) CSG_CUDA(cudaStreamWaitEvent(st, ctx.ev[6], 0));
+  bucket_count_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl, chunk, phase == PHASE_REST);
   CSG_CUDA(cudaGetLastError());
   bucket_scan_kernel<<<1, 32, 0, st>>>(s.ctrl);
   CSG_CUDA(cudaGetLastError());
-  row_list_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl, s.row_list);
+  row_list_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl, s.row_list, chunk, phase == PHASE_REST);
   CSG_CUDA(cudaGetLastError());
   count_launches(7 + 3 * a.passes);
   return true;
