@@ -60,6 +60,17 @@ class Context:
     def workspace_bytes(self):
         return int(_lib.load().sporder_context_workspace_bytes(self._h))
 
+    def set_stream_limit(self, max_elements):
+        """Upper bound (stream elements of 8 bytes, 0 = none) on the buffer for the heaviest
+        rows' materialised candidate streams; results never depend on it."""
+        _lib.load().sporder_context_set_stream_limit(self._h, int(max_elements))
+
+    def set_ahead_threshold(self, min_nnz):
+        """Nonzeros from which a csg call runs its heaviest chunk ahead of the rest on a second
+        stream: 0 = the built-in rule, > 0 = every call of at least that many nonzeros, < 0 =
+        never.  Results never depend on it."""
+        _lib.load().sporder_context_set_ahead_threshold(self._h, int(min_nnz))
+
     def close(self):
         if getattr(self, "_h", None):
             _lib.load().sporder_context_destroy(self._h)

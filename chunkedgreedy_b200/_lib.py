@@ -57,6 +57,7 @@ SYMBOLS = {
     "sporder_context_set_stream": (None, [_P, _P]),
     "sporder_context_workspace_bytes": (C.c_uint64, [_P]),
     "sporder_context_set_stream_limit": (None, [_P, C.c_uint64]),
+    "sporder_context_set_ahead_threshold": (None, [_P, C.c_int64]),
     "sporder_csg_with_table": (C.c_int32, [_P, C.c_int32, C.c_int32, _P, _P, C.c_bool, C.c_int32,
                                            C.c_float, C.c_int32, _P, _P, C.c_uint64,
                                            C.POINTER(CsgTiming), C.POINTER(CsgStats)]),

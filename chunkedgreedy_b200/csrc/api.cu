@@ -332,9 +332,18 @@ bool run_csg(Context &ctx, int32_t n, int32_t ncols, int32_t row_base, int32_t n
   // that chunk is transposed first, on a second stream, and its heavy rows' chains start
   // there while the context's stream transposes everything else; the two meet before the
   // greedy stage.  Results do not depend on the split (the same kernels on the same rows).
+  // By default for calls of 2^24 nonzeros in 64 chunks or more, whose chunk ahead must hold 2^17
+  // nonzeros: smaller calls do not pay for the second pipeline's fifteen launches.  A caller's
+  // own threshold (sporder_context_set_ahead_threshold) applies to any call of two chunks.
   const int64_t chunks = (static_cast<int64_t>(n) + p.chunk - 1) / p.chunk;
-  const bool ahead = !sym_path && ctx.side_stream != nullptr && nnz >= AHEAD_MIN_NNZ && chunks >= 64 &&
-                     p.chunk <= 4096 && std::getenv("SPORDER_B200_NO_AHEAD") == nullptr;
+  bool ahead = !sym_path && ctx.side_stream != nullptr && p.chunk <= 4096;
+  int32_t ahead_chunk_nnz = 1 << 17;
+  if (ctx.ahead_min_nnz == 0) {
+    ahead = ahead && nnz >= AHEAD_MIN_NNZ && chunks >= 64;
+  } else {
+    ahead = ahead && ctx.ahead_min_nnz > 0 && nnz >= ctx.ahead_min_nnz && chunks >= 2;
+    ahead_chunk_nnz = 0;
+  }
   CsgScratch s, sp;
   if (!plan_scratch(ctx, n, nnz, p, d_table, &s, 0, false, ahead ? &sp : nullptr)) return false;
   cudaStream_t st = ctx.stream;
@@ -348,7 +357,7 @@ bool run_csg(Context &ctx, int32_t n, int32_t ncols, int32_t row_base, int32_t n
   } else {
     if (zero_table)
       CSG_CUDA(cudaMemsetAsync(s.table, 0, sizeof(uint64_t) * static_cast<size_t>(n) * p.k, st));
-    if (!launch_priority_pick(ctx, n, nnz, p.chunk, d_ptr, s, sp)) return false;
+    if (!launch_priority_pick(ctx, n, nnz, p.chunk, d_ptr, s, sp, ahead_chunk_nnz)) return false;
     CSG_CUDA(cudaEventRecord(ctx.ev[5], st));
     CSG_CUDA(cudaStreamWaitEvent(ctx.side_stream, ctx.ev[5], 0));
     // the chunk ahead: queued first, so that the host's launches of the rest do not delay it
@@ -639,6 +648,10 @@ void sporder_context_set_stream(sporder_context_t h, void *stream) {
   // previous stream (sporder_spmm_async) must be over before another stream may reuse them.
   if (next != h->c.stream) cudaStreamSynchronize(h->c.stream);
   h->c.stream = next;
+}
+
+void sporder_context_set_ahead_threshold(sporder_context_t h, int64_t min_nnz) {
+  if (h) h->c.ahead_min_nnz = min_nnz;
 }
 
 void sporder_context_set_stream_limit(sporder_context_t h, uint64_t max_elements) {

@@ -62,6 +62,9 @@ struct Context {
   // Second stream (higher priority) for the part of a large call that runs ahead of the rest:
   // the transposition and the chains of the chunk that holds the most nonzeros (see run_csg).
   cudaStream_t side_stream = nullptr;
+  // nonzeros from which a call runs one chunk ahead: 0 = the built-in threshold, negative =
+  // never, positive = the caller's threshold (sporder_context_set_ahead_threshold)
+  int64_t ahead_min_nnz = 0;
   uint64_t stream_limit = 0;       // caller's upper bound (sporder_context_set_stream_limit), 0 = none
 };
 
@@ -147,7 +150,7 @@ bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32
                       uint32_t *ctrl_main = nullptr);
 // start of a call that runs one chunk ahead: clears the counters of both parts and names the chunk
 bool launch_priority_pick(Context &ctx, int32_t n, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
-                          CsgScratch &s, CsgScratch &prio);
+                          CsgScratch &s, CsgScratch &prio, int32_t min_chunk_nnz);
 bool launch_sketch(Context &ctx, int32_t n, int32_t nnz, const CsgParams &p, const int32_t *d_ptr,
                    CsgScratch &s, int32_t row_base, bool zero_table, int phase = PHASE_ALL);
 bool launch_greedy(Context &ctx, int32_t n, const CsgParams &p, CsgScratch &s,

@@ -317,10 +317,9 @@ __global__ void classify_chunks_kernel(TransposeArgs a) {
 }
 
 // The chunk that runs ahead of the rest: the one with the most nonzeros, if it is a heavy
-// chunk of at least PRIO_MIN_NNZ nonzeros (a row that streams 65,536 candidates or more
-// needs a chunk about that big).  It becomes the only entry of `ap`'s list of heavy chunks.
-constexpr int32_t PRIO_MIN_NNZ = 1 << 17;
-__global__ void __launch_bounds__(1024) pick_priority_kernel(TransposeArgs a, TransposeArgs ap) {
+// chunk of at least min_nnz nonzeros (a row that streams 65,536 candidates or more needs a
+// chunk about that big).  It becomes the only entry of `ap`'s list of heavy chunks.
+__global__ void __launch_bounds__(1024) pick_priority_kernel(TransposeArgs a, TransposeArgs ap, int32_t min_nnz) {
   __shared__ unsigned long long best[32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   unsigned long long mine = 0;  // (nonzeros << 32) | ~chunk: the first of equally heavy chunks wins
@@ -340,7 +339,7 @@ __global__ void __launch_bounds__(1024) pick_priority_kernel(TransposeArgs a, Tr
     for (int w = 1; w < 32; ++w) mine = best[w] > mine ? best[w] : mine;
     const int32_t L = static_cast<int32_t>(mine >> 32);
     const uint32_t q = 0xFFFFFFFFu - static_cast<uint32_t>(mine);
-    const bool on = L > T_LS && L >= PRIO_MIN_NNZ;
+    const bool on = L > T_LS && L >= min_nnz;
     a.ctrl[CTRL_PRIO] = on ? q : PRIO_NONE;
     ap.ctrl[CTRL_PRIO] = on ? q : PRIO_NONE;
     ap.ctrl[CTRL_HEAVY_COUNT] = on ? 1u : 0u;
@@ -845,14 +844,14 @@ TransposeArgs transpose_args(int32_t n, int32_t ncols, int32_t nnz, int32_t chun
 }  // namespace
 
 bool launch_priority_pick(Context &ctx, int32_t n, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
-                          CsgScratch &s, CsgScratch &prio) {
+                          CsgScratch &s, CsgScratch &prio, int32_t min_chunk_nnz) {
   const TransposeArgs a = transpose_args(n, n, nnz, chunk, d_ptr, nullptr, s);
   const TransposeArgs ap = transpose_args(n, n, nnz, chunk, d_ptr, nullptr, prio);
   cudaStream_t st = ctx.stream;
   CSG_CUDA(cudaMemsetAsync(s.ctrl, 0, sizeof(uint32_t) * CTRL_WORDS, st));
   CSG_CUDA(cudaMemsetAsync(prio.ctrl, 0, sizeof(uint32_t) * CTRL_WORDS, st));
   CSG_CUDA(cudaMemsetAsync(s.row_work, 0, sizeof(uint32_t) * static_cast<size_t>(n), st));
-  pick_priority_kernel<<<1, 1024, 0, st>>>(a, ap);
+  pick_priority_kernel<<<1, 1024, 0, st>>>(a, ap, min_chunk_nnz);
   CSG_CUDA(cudaGetLastError());
   count_launches(1);
   return true;

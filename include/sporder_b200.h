@@ -181,6 +181,15 @@ SPORDER_API void sporder_context_set_stream(sporder_context_t ctx, void *stream)
  * computed by the kernel of the lighter rows; results are the same for every bound. */
 SPORDER_API void sporder_context_set_stream_limit(sporder_context_t ctx, uint64_t max_elements);
 
+/* Calls of sporder_chunk_similarity_greedy (and its variants with a table, on host buffers or
+ * on a row shard) with many nonzeros run the chunk that holds the most of them ahead of the
+ * rest, on a second stream of the context: that chunk's transposition first, then the
+ * chains of its heaviest rows, while everything else is still being transposed.  min_nnz
+ * = 0: the built-in rule (2^24 nonzeros and 64 chunks or more); > 0: every call of at least
+ * min_nnz nonzeros and two chunks; < 0: never.  Results are the same either way.  No
+ * reference counterpart. */
+SPORDER_API void sporder_context_set_ahead_threshold(sporder_context_t ctx, int64_t min_nnz);
+
 /* Bytes of device workspace the context currently holds (grow-only cache). */
 SPORDER_API uint64_t sporder_context_workspace_bytes(sporder_context_t ctx);
 

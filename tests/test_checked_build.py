@@ -35,6 +35,13 @@ for name in names:
     rp, ri, rv = oracle.reorder(ptr, ind, o, val, symmetric=True)
     assert np.array_equal(i2.cpu().numpy(), ri) and np.array_equal(v2.cpu().numpy(), rv), name
     assert sp.count_pillars(dp, di, 16) == oracle.count_pillars(ptr, ind, 16), name
+    # the route that runs one chunk ahead on a second stream, forced for every size
+    ctxa = sp.Context()
+    ctxa.set_ahead_threshold(1)
+    for _ in range(2):
+        o3, t3 = sp.csg_table(dp, di, is_symmetric=False, ctx=ctxa, **params)
+        assert np.array_equal(t3.cpu().numpy().view(np.uint64), t) and np.array_equal(o3.cpu().numpy(), o), name
+    ctxa.close()
     if not sym:  # a false promise of symmetry: garbage candidates, but every index in bounds
         o2 = sp.chunk_similarity_greedy(dp, di, is_symmetric=True, **params)
         assert np.array_equal(np.sort(o2.cpu().numpy()), np.arange(ptr.size - 1)), name

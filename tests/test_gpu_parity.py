@@ -515,6 +515,59 @@ def test_heavy_rows_that_do_not_fit_the_stream_buffer_take_the_light_path():
         ctx.close()
 
 
+AHEAD_CASES = ["rmat12", "hubsym", "ragged", "m96", "m512", "bigchunk", "dense_ties", "dense_fill",
+               "dense_ragged", "dense_c4096", "dense_m128", "dense_m256", "rmat16"]
+
+
+@pytest.mark.parametrize("name", AHEAD_CASES)
+def test_running_one_chunk_ahead_changes_nothing(name):
+    # Large calls transpose the chunk with the most nonzeros first and start the chains of
+    # its heaviest rows on a second stream while the rest is transposed.  With the threshold
+    # at one nonzero every call of two chunks takes that route, whatever its size: same table,
+    # same permutation as the CPU restatement, on a first call (stream buffer cut in halves)
+    # and on later ones (cut by what each part asked for); and the same with the route closed.
+    sp = _sp()
+    ptr, ind, val, sym, params = cases.build(name)
+    o_or, t_or = oracle.csg(ptr, ind, False, with_table=True, **params)
+    ctx = sp.Context()
+    ctx.set_ahead_threshold(1)
+    for _ in range(3):
+        order, table = sp.csg_table(_dev(ptr), _dev(ind), ctx=ctx, **params)
+        assert np.array_equal(table.cpu().numpy().view(np.uint64), t_or), name
+        assert np.array_equal(order.cpu().numpy(), o_or), name
+    ctx.set_stream_limit(200_000)  # ... and with both parts short of room for their streams
+    order, table = sp.csg_table(_dev(ptr), _dev(ind), ctx=ctx, **params)
+    assert np.array_equal(table.cpu().numpy().view(np.uint64), t_or), name
+    ctx.set_stream_limit(0)
+    ctx.set_ahead_threshold(-1)
+    order, table = sp.csg_table(_dev(ptr), _dev(ind), ctx=ctx, **params)
+    assert np.array_equal(table.cpu().numpy().view(np.uint64), t_or), name
+    assert np.array_equal(order.cpu().numpy(), o_or), name
+    ctx.close()
+
+
+def test_running_one_chunk_ahead_at_scale_20_and_with_statistics():
+    # R-MAT scale 20 (15.5 M nonzeros, 1024 chunks): chunk 0 holds the rows with the longest
+    # streams, which is the case the route is made for
+    sp = _sp()
+    from chunkedgreedy_b200 import synth
+    ptr, ind, val = synth.rmat(scale=20, edge_factor=16, seed=3)
+    dp, di = _dev(ptr), _dev(ind)
+    plain = sp.Context()
+    plain.set_ahead_threshold(-1)
+    o0, t0 = sp.csg_table(dp, di, ctx=plain)
+    ahead = sp.Context()
+    ahead.set_ahead_threshold(1)
+    for _ in range(2):
+        o1, t1 = sp.csg_table(dp, di, ctx=ahead)
+        assert torch.equal(t1, t0) and torch.equal(o1, o0)
+    o2, tm, st = sp.chunk_similarity_greedy(dp, di, ctx=ahead, with_timing=True, with_stats=True)
+    _, _, st0 = sp.chunk_similarity_greedy(dp, di, ctx=plain, with_timing=True, with_stats=True)
+    assert torch.equal(o2, o0) and st == st0 and tm["wall_ms"] > 0
+    plain.close()
+    ahead.close()
+
+
 def test_workspace_is_in_proportion_to_the_input():
     # a small matrix must not make the context hold the gigabyte a large one needs
     sp = _sp()
