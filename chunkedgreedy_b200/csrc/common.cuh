@@ -128,6 +128,8 @@ enum {
   CTRL_CHECK = 13,         // checked build: site of the first index out of bounds, then the index (64-bit)
   CTRL_BUCKET_COUNT = 16,  // 33 entries
   CTRL_PRIO = 50,          // chunk whose heavy rows run ahead of the rest (PRIO_NONE: no such chunk)
+  CTRL_CRITICAL_ROWS = 51,  // rows at the head of the chunk ahead's list whose chains keep a scheduler each
+  CTRL_CRITICAL_TICKET = 52,
   CTRL_BUCKET_BASE = 56,   // 33 entries
   CTRL_BUCKET_FILL = 96,   // 33 entries
   CTRL_STATS = 136,        // see greedy.cu (8-byte aligned)

@@ -1425,21 +1425,25 @@ __device__ __noinline__ void rounds_row(const int2 *in, uint32_t total, int32_t 
   __syncwarp();
 }
 
-template <int CELLS>
-__global__ void __launch_bounds__(S_THREADS, 1) heavy_rounds_kernel(SketchArgs a, int tab_bytes, int mates_words) {
+// WARPS per block: four (a scheduler each) for the chains that decide how long the call
+// takes; eight, two to a scheduler, for the chains of the rest of a call that runs one chunk
+// ahead - they have time to spare and then hold half as many SMs.
+template <int CELLS, int WARPS>
+__global__ void __launch_bounds__(32 * WARPS, 1) heavy_rounds_kernel(SketchArgs a, int tab_bytes, int mates_words) {
   // dynamic shared memory: two stream buffers per warp (the next batch lands while this
   // one is consumed), then the key tables
   extern __shared__ __align__(16) unsigned char heavy_dyn[];
+  constexpr int RING_BYTES = WARPS * 2 * H_RING * 8;
   int2(*rings)[2][H_RING] = reinterpret_cast<int2(*)[2][H_RING]>(heavy_dyn);
-  __shared__ RoundState<CELLS> state[S_WARPS];
+  __shared__ RoundState<CELLS> state[WARPS];
   const int lane = lane_id(), warp = threadIdx.x >> 5;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t heavy = a.ctrl[CTRL_HEAVY_ROWS];
-  uint8_t *tab = heavy_dyn + ROUND_RING_BYTES + static_cast<size_t>(warp) * tab_bytes;
+  uint8_t *tab = heavy_dyn + RING_BYTES + static_cast<size_t>(warp) * tab_bytes;
   // (behind the four key tables: a word per row of the chunk and warp for round_window's
   // duplicate detection, when it fits)
   uint32_t *mates = mates_words > 0
-                        ? reinterpret_cast<uint32_t *>(heavy_dyn + ROUND_RING_BYTES + static_cast<size_t>(S_WARPS) * tab_bytes) +
+                        ? reinterpret_cast<uint32_t *>(heavy_dyn + RING_BYTES + static_cast<size_t>(WARPS) * tab_bytes) +
                               static_cast<size_t>(warp) * mates_words
                         : nullptr;
   for (int i = lane; i < mates_words; i += 32) mates[i] = 0u;
@@ -1452,11 +1456,22 @@ __global__ void __launch_bounds__(S_THREADS, 1) heavy_rounds_kernel(SketchArgs a
   __syncwarp();
 #endif
   for (int i = lane * 16; i < tab_bytes; i += 32 * 16) *reinterpret_cast<uint4 *>(tab + i) = make_uint4(0, 0, 0, 0);
+  // Blocks of eight warps: the first blocks take the critical rows at the head of the list with
+  // four of their warps (the other four leave at once, so those chains have a scheduler each);
+  // all other blocks share the rest of the list among eight warps.
+  uint32_t crit = 0;
+  if (WARPS > S_WARPS) {
+    crit = a.ctrl[CTRL_CRITICAL_ROWS];
+    crit = crit < heavy ? crit : heavy;
+  }
+  const bool sparse = WARPS > S_WARPS && blockIdx.x < (crit + S_WARPS - 1) / S_WARPS;
+  if (sparse && warp >= S_WARPS) return;
   for (;;) {
     uint32_t item = 0;
-    if (lane == 0) item = atomicAdd(&a.ctrl[CTRL_HEAVY_TICKET + 1], 1u);
+    if (lane == 0)
+      item = sparse ? atomicAdd(&a.ctrl[CTRL_CRITICAL_TICKET], 1u) : crit + atomicAdd(&a.ctrl[CTRL_HEAVY_TICKET + 1], 1u);
     item = __shfl_sync(FULL, item, 0);
-    if (item >= heavy) break;
+    if (item >= (sparse ? crit : heavy)) break;
     const int32_t r = a.row_list[item];
     // checked build: the row, its place in the state array and its stream's extent
     if (!index_ok(a.ctrl, CHK_LIST, r, a.n) || !index_ok(a.ctrl, CHK_STATE, item, a.heavy_max) ||
@@ -1533,23 +1548,34 @@ bool launch_cells(Context &ctx, const SketchArgs &a, int phase) {
   // tables for a block's four warps (one byte per row of a chunk each) when they fit in there.
   bool in_rounds = false;
   if constexpr (CELLS <= ROUND_CELLS) {
-    cudaFuncAttributes fa;
-    CSG_CUDA(cudaFuncGetAttributes(&fa, heavy_rounds_kernel<CELLS>));
-    const int pad = ctx.smem_optin - 1024 - static_cast<int>(fa.sharedSizeBytes);
-    int64_t tab_bytes = (static_cast<int64_t>(a.chunk) + 15) / 16 * 16;
-    if (ROUND_RING_BYTES + tab_bytes * S_WARPS > pad) tab_bytes = 0;  // slots found by comparing keys
-    // round_window's duplicate detector: four bytes per row of the chunk and warp, if they fit too
-    int64_t mates_words = tab_bytes;
-    if (tab_bytes == 0 || ROUND_RING_BYTES + 5 * tab_bytes * S_WARPS > pad) mates_words = 0;
-
-    {
-      CSG_CUDA(cudaFuncSetAttribute(heavy_rounds_kernel<CELLS>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, pad));
-      heavy_rounds_kernel<CELLS><<<chain_blocks, S_THREADS, pad, st>>>(a, static_cast<int>(tab_bytes),
-                                                                     static_cast<int>(mates_words));
+    auto launch_rounds = [&](auto kernel, int warps, int blocks, bool must_fit, bool *launched) -> bool {
+      cudaFuncAttributes fa;
+      CSG_CUDA(cudaFuncGetAttributes(&fa, kernel));
+      const int pad = ctx.smem_optin - 1024 - static_cast<int>(fa.sharedSizeBytes);
+      const int64_t ring_bytes = static_cast<int64_t>(warps) * 2 * H_RING * 8;
+      int64_t tab_bytes = (static_cast<int64_t>(a.chunk) + 15) / 16 * 16;
+      if (ring_bytes + tab_bytes * warps > pad) tab_bytes = 0;  // slots found by comparing keys
+      // round_window's duplicate detector: four bytes per row of the chunk and warp, if they fit too
+      int64_t mates_words = tab_bytes;
+      if (tab_bytes == 0 || ring_bytes + 5 * tab_bytes * warps > pad) mates_words = 0;
+      *launched = false;
+      if (must_fit && (mates_words == 0 || pad < ring_bytes)) return true;  // (the caller falls back)
+      CSG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pad));
+      kernel<<<blocks, 32 * warps, pad, st>>>(a, static_cast<int>(tab_bytes), static_cast<int>(mates_words));
       CSG_CUDA(cudaGetLastError());
-      in_rounds = true;
+      *launched = true;
+      return true;
+    };
+    if (phase != PHASE_ALL && CELLS == WINDOW_CELLS) {
+      // eight chains to an SM, if all their tables fit: the rest of the call on half as many
+      // SMs; the chunk ahead with its critical rows apart (see the kernel)
+      const int blocks = phase == PHASE_REST ? (chain_blocks + 1) / 2 : chain_blocks;
+      if (!launch_rounds(heavy_rounds_kernel<CELLS, 2 * S_WARPS>, 2 * S_WARPS, blocks, true, &in_rounds))
+        return false;
     }
+    if (!in_rounds &&
+        !launch_rounds(heavy_rounds_kernel<CELLS, S_WARPS>, S_WARPS, chain_blocks, false, &in_rounds))
+      return false;
   }
   if (!in_rounds) {
     const int pad = ctx.smem_optin - 1024 - 2 * S_WARPS * S_RING * 4;

@@ -347,24 +347,42 @@ __global__ void __launch_bounds__(1024) pick_priority_kernel(TransposeArgs a, Tr
   }
 }
 
-// Work list of the chunk ahead: its rows that stream 65,536 candidates or more, heaviest
-// bucket first (the other rows of the chunk go with everybody else's).  One block.
+// Work list of the chunk ahead: its rows that stream 65,536 candidates or more (the other
+// rows of the chunk go with everybody else's).  First the critical rows - at least half as
+// long as the longest, the ones that can decide when the call ends; their chains keep a
+// scheduler to themselves - then the others, heaviest bucket first.  One block.
 __global__ void __launch_bounds__(1024) priority_rows_kernel(TransposeArgs ap, int32_t *row_list) {
-  __shared__ uint32_t count;
+  __shared__ uint32_t count, longest, critical;
   __shared__ unsigned long long need;
   if (threadIdx.x == 0) {
     count = 0;
     need = 0;
+    longest = 0;
+    critical = 0;
   }
   __syncthreads();
   const uint32_t prio = ap.ctrl[CTRL_PRIO];
   if (prio != PRIO_NONE) {
     const int64_t start = static_cast<int64_t>(prio) * ap.chunk;
     const int64_t end = start + ap.chunk < ap.n ? start + ap.chunk : ap.n;
+    for (int64_t r = start + threadIdx.x; r < end; r += blockDim.x) atomicMax(&longest, ap.row_work[r]);
+    __syncthreads();
+    uint32_t bar = longest - longest / 2;
+    if (bar < (1u << (SKETCH_HEAVY_BUCKET - 1))) bar = 1u << (SKETCH_HEAVY_BUCKET - 1);
+    for (int64_t r = start + threadIdx.x; r < end; r += blockDim.x) {
+      const uint32_t t = ap.row_work[r];
+      if (t >= bar) {
+        row_list[atomicAdd(&count, 1u)] = static_cast<int32_t>(r);
+        atomicAdd(&need, static_cast<unsigned long long>(t));
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) critical = count;
+    __syncthreads();
     for (int b = 32; b >= SKETCH_HEAVY_BUCKET; --b) {
       for (int64_t r = start + threadIdx.x; r < end; r += blockDim.x) {
         const uint32_t t = ap.row_work[r];
-        if (t && 32 - __clz(t) == b) {
+        if (t && t < bar && 32 - __clz(t) == b) {
           row_list[atomicAdd(&count, 1u)] = static_cast<int32_t>(r);
           atomicAdd(&need, static_cast<unsigned long long>(t));
         }
@@ -375,6 +393,8 @@ __global__ void __launch_bounds__(1024) priority_rows_kernel(TransposeArgs ap, i
   if (threadIdx.x == 0) {
     ap.ctrl[CTRL_ROWS_LISTED] = count;
     ap.ctrl[CTRL_HEAVY_ROWS] = count;
+    ap.ctrl[CTRL_CRITICAL_ROWS] = critical;
+    ap.ctrl[CTRL_CRITICAL_TICKET] = 0;
     ap.ctrl[CTRL_ROW_TICKET] = count;
     ap.ctrl[CTRL_HEAVY_TICKET] = 0;
     ap.ctrl[CTRL_HEAVY_TICKET + 1] = 0;
