@@ -364,7 +364,7 @@ bool run_csg(Context &ctx, int32_t n, int32_t ncols, int32_t row_base, int32_t n
     if (!launch_transpose(ctx, n, ncols, nnz, p.chunk, d_ptr, d_ind, sp, false, PHASE_PRIO, s.ctrl)) return false;
     if (!launch_sketch(ctx, n, nnz, p, d_ptr, sp, row_base, false, PHASE_PRIO)) return false;
     CSG_CUDA(cudaEventRecord(ctx.ev[7], ctx.side_stream));
-    if (!launch_transpose(ctx, n, ncols, nnz, p.chunk, d_ptr, d_ind, s, false, PHASE_REST)) return false;
+    if (!launch_transpose(ctx, n, ncols, nnz, p.chunk, d_ptr, d_ind, s, false, PHASE_REST, sp.ctrl)) return false;
     if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
     CSG_CUDA(cudaStreamWaitEvent(st, ctx.ev[8], 0));
     if (!launch_sketch(ctx, n, nnz, p, d_ptr, s, row_base, false, PHASE_REST)) return false;

@@ -130,6 +130,7 @@ enum {
   CTRL_PRIO = 50,          // chunk whose heavy rows run ahead of the rest (PRIO_NONE: no such chunk)
   CTRL_CRITICAL_ROWS = 51,  // rows at the head of the chunk ahead's list whose chains keep a scheduler each
   CTRL_CRITICAL_TICKET = 52,
+  CTRL_LONGEST = 53,       // longest candidate stream of the chunk ahead
   CTRL_BUCKET_BASE = 56,   // 33 entries
   CTRL_BUCKET_FILL = 96,   // 33 entries
   CTRL_STATS = 136,        // see greedy.cu (8-byte aligned)
@@ -149,7 +150,7 @@ constexpr int SKETCH_HEAVY_BUCKET = 17;  // rows streaming >= 65536 candidates a
 // stage launchers; all enqueue on ctx.stream and return false after set_error()
 bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
                       const int32_t *d_ind, CsgScratch &s, bool symmetric = false, int phase = PHASE_ALL,
-                      uint32_t *ctrl_main = nullptr);
+                      uint32_t *ctrl_other = nullptr);
 // start of a call that runs one chunk ahead: clears the counters of both parts and names the chunk
 bool launch_priority_pick(Context &ctx, int32_t n, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
                           CsgScratch &s, CsgScratch &prio, int32_t min_chunk_nnz);

@@ -1456,22 +1456,36 @@ __global__ void __launch_bounds__(32 * WARPS, 1) heavy_rounds_kernel(SketchArgs 
   __syncwarp();
 #endif
   for (int i = lane * 16; i < tab_bytes; i += 32 * 16) *reinterpret_cast<uint4 *>(tab + i) = make_uint4(0, 0, 0, 0);
-  // Blocks of eight warps: the first blocks take the critical rows at the head of the list with
-  // four of their warps (the other four leave at once, so those chains have a scheduler each);
-  // all other blocks share the rest of the list among eight warps.
-  uint32_t crit = 0;
+  // Blocks of eight warps (a call that runs one chunk ahead): the first blocks take the critical
+  // rows at the head of the list with four of their warps (the other four leave at once, so
+  // those chains have a scheduler each); the blocks behind them take the other rows eight at a
+  // time, in list order, so that the rows fill as few SMs as they can and blocks without rows
+  // leave at once.  Blocks of four warps draw tickets.
+  uint32_t item = 0, stride = 0, last = heavy;
   if (WARPS > S_WARPS) {
-    crit = a.ctrl[CTRL_CRITICAL_ROWS];
+    uint32_t crit = a.ctrl[CTRL_CRITICAL_ROWS];
     crit = crit < heavy ? crit : heavy;
+    uint32_t sparse_blocks = (crit + S_WARPS - 1) / S_WARPS;
+    if (sparse_blocks >= gridDim.x) {  // no block left for other rows: all rows alike
+      sparse_blocks = gridDim.x;
+      crit = heavy;
+    }
+    if (blockIdx.x < sparse_blocks) {
+      if (warp >= S_WARPS) return;
+      item = blockIdx.x * S_WARPS + warp;
+      stride = sparse_blocks * S_WARPS;
+      last = crit;
+    } else {
+      item = crit + (blockIdx.x - sparse_blocks) * WARPS + warp;
+      stride = (gridDim.x - sparse_blocks) * WARPS;
+    }
   }
-  const bool sparse = WARPS > S_WARPS && blockIdx.x < (crit + S_WARPS - 1) / S_WARPS;
-  if (sparse && warp >= S_WARPS) return;
-  for (;;) {
-    uint32_t item = 0;
-    if (lane == 0)
-      item = sparse ? atomicAdd(&a.ctrl[CTRL_CRITICAL_TICKET], 1u) : crit + atomicAdd(&a.ctrl[CTRL_HEAVY_TICKET + 1], 1u);
-    item = __shfl_sync(FULL, item, 0);
-    if (item >= (sparse ? crit : heavy)) break;
+  for (;; item += stride) {
+    if (WARPS == S_WARPS) {
+      if (lane == 0) item = atomicAdd(&a.ctrl[CTRL_HEAVY_TICKET + 1], 1u);
+      item = __shfl_sync(FULL, item, 0);
+    }
+    if (item >= last) break;
     const int32_t r = a.row_list[item];
     // checked build: the row, its place in the state array and its stream's extent
     if (!index_ok(a.ctrl, CHK_LIST, r, a.n) || !index_ok(a.ctrl, CHK_STATE, item, a.heavy_max) ||
@@ -1567,10 +1581,8 @@ bool launch_cells(Context &ctx, const SketchArgs &a, int phase) {
       return true;
     };
     if (phase != PHASE_ALL && CELLS == WINDOW_CELLS) {
-      // eight chains to an SM, if all their tables fit: the rest of the call on half as many
-      // SMs; the chunk ahead with its critical rows apart (see the kernel)
-      const int blocks = phase == PHASE_REST ? (chain_blocks + 1) / 2 : chain_blocks;
-      if (!launch_rounds(heavy_rounds_kernel<CELLS, 2 * S_WARPS>, 2 * S_WARPS, blocks, true, &in_rounds))
+      // eight chains to an SM, if all their tables fit, critical rows apart (see the kernel)
+      if (!launch_rounds(heavy_rounds_kernel<CELLS, 2 * S_WARPS>, 2 * S_WARPS, chain_blocks, true, &in_rounds))
         return false;
     }
     if (!in_rounds &&

@@ -395,6 +395,7 @@ __global__ void __launch_bounds__(1024) priority_rows_kernel(TransposeArgs ap, i
     ap.ctrl[CTRL_HEAVY_ROWS] = count;
     ap.ctrl[CTRL_CRITICAL_ROWS] = critical;
     ap.ctrl[CTRL_CRITICAL_TICKET] = 0;
+    ap.ctrl[CTRL_LONGEST] = longest;
     ap.ctrl[CTRL_ROW_TICKET] = count;
     ap.ctrl[CTRL_HEAVY_TICKET] = 0;
     ap.ctrl[CTRL_HEAVY_TICKET + 1] = 0;
@@ -790,13 +791,27 @@ __global__ void __launch_bounds__(256) bucket_count_kernel(int32_t n, const uint
 }
 
 // Heaviest bucket first: rows with 2^(b-1) <= work < 2^b sit in bucket b.
-__global__ void bucket_scan_kernel(uint32_t *ctrl) {
+// ctrl_ahead: the control words of the chunk that runs ahead, when the call has one.  The rows
+// of this list that are within a factor of four of the longest stream of the whole call (their
+// bucket is the top one or the one below) count as critical like the long rows of the chunk
+// ahead: their chains keep a scheduler to themselves (see heavy_rounds_kernel).
+__global__ void bucket_scan_kernel(uint32_t *ctrl, const uint32_t *ctrl_ahead) {
   if (threadIdx.x == 0) {
     uint32_t run = 0;
+    int top = 0;
     for (int b = 32; b >= 1; --b) {
       ctrl[CTRL_BUCKET_BASE + b] = run;
       run += ctrl[CTRL_BUCKET_COUNT + b];
       ctrl[CTRL_BUCKET_FILL + b] = 0;
+      if (top == 0 && ctrl[CTRL_BUCKET_COUNT + b]) top = b;
+    }
+    if (ctrl_ahead) {
+      const uint32_t longest = ctrl_ahead[CTRL_LONGEST];
+      const int top_ahead = longest ? 32 - __clz(longest) : 0;
+      top = top_ahead > top ? top_ahead : top;
+      int from = top - 1 > SKETCH_HEAVY_BUCKET ? top - 1 : SKETCH_HEAVY_BUCKET;
+      ctrl[CTRL_CRITICAL_ROWS] = from <= 32 ? ctrl[CTRL_BUCKET_BASE + from - 1] : 0u;  // rows of buckets >= from
+      ctrl[CTRL_CRITICAL_TICKET] = 0;
     }
     ctrl[CTRL_ROWS_LISTED] = run;
     // rows with at least 2^(SKETCH_HEAVY_BUCKET-1) stream elements head the list; the
@@ -883,9 +898,11 @@ bool launch_priority_pick(Context &ctx, int32_t n, int32_t nnz, int32_t chunk, c
 // PHASE_REST (context's stream): every other chunk, then - once ev[6] has passed, because the
 // lists read the work counters of all rows - the lists of everything the part ahead left.
 bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32_t chunk, const int32_t *d_ptr,
-                      const int32_t *d_ind, CsgScratch &s, bool symmetric, int phase, uint32_t *ctrl_main) {
+                      const int32_t *d_ind, CsgScratch &s, bool symmetric, int phase, uint32_t *ctrl_other) {
+  // ctrl_other: the control words of the other part of a call that runs one chunk ahead
   TransposeArgs a = transpose_args(n, ncols, nnz, chunk, d_ptr, d_ind, s);
-  a.ctrl_main = ctrl_main ? ctrl_main : s.ctrl;
+  a.ctrl_main = phase == PHASE_PRIO && ctrl_other ? ctrl_other : s.ctrl;
+  const uint32_t *ctrl_ahead = phase == PHASE_REST ? ctrl_other : nullptr;
   a.skip_prio = phase == PHASE_REST;
   const size_t smem = sizeof(Shared);
   CSG_CUDA(cudaFuncSetAttribute(transpose_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -905,7 +922,7 @@ bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32
     CSG_CUDA(cudaGetLastError());
     bucket_count_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl, chunk, false);
     CSG_CUDA(cudaGetLastError());
-    bucket_scan_kernel<<<1, 32, 0, st>>>(s.ctrl);
+    bucket_scan_kernel<<<1, 32, 0, st>>>(s.ctrl, nullptr);
     CSG_CUDA(cudaGetLastError());
     row_list_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl, s.row_list, chunk, false);
     CSG_CUDA(cudaGetLastError());
@@ -935,9 +952,9 @@ bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32
   heavy_emit_kernel<<<hgrid * 2, T_THREADS, 0, st>>>(a);
   CSG_CUDA(cudaGetLastError());
   if (phase == PHASE_PRIO) {
-    CSG_CUDA(cudaEventRecord(ctx.ev[6], st));
     priority_rows_kernel<<<1, 1024, 0, st>>>(a, s.row_list);
     CSG_CUDA(cudaGetLastError());
+    CSG_CUDA(cudaEventRecord(ctx.ev[6], st));  // the rest may read this chunk's work counters and its longest stream
     count_launches(3 + 3 * a.passes);
     return true;
   }
@@ -947,7 +964,7 @@ bool launch_transpose(Context &ctx, int32_t n, int32_t ncols, int32_t nnz, int32
   if (phase == PHASE_REST) CSG_CUDA(cudaStreamWaitEvent(st, ctx.ev[6], 0));
   bucket_count_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl, chunk, phase == PHASE_REST);
   CSG_CUDA(cudaGetLastError());
-  bucket_scan_kernel<<<1, 32, 0, st>>>(s.ctrl);
+  bucket_scan_kernel<<<1, 32, 0, st>>>(s.ctrl, phase == PHASE_REST ? ctrl_ahead : nullptr);
   CSG_CUDA(cudaGetLastError());
   row_list_kernel<<<lgrid, 256, 0, st>>>(n, s.row_work, s.ctrl, s.row_list, chunk, phase == PHASE_REST);
   CSG_CUDA(cudaGetLastError());
