@@ -452,7 +452,7 @@ def run_ours(args, rank, world, local_rank):
 # DRAM bytes (read + write) of the sketch stage's kernels per csg call at full size, from an
 # ncu capture of `bench.py --steps 1 --warmup 1 --no-ref-cuda --no-cpu-baseline --no-spmm`;
 # a number of the build it was captured on, not of this run
-TRAFFIC_RMAT22 = 4543846656
+TRAFFIC_RMAT22 = 4454053376
 TRAFFIC_NOTE = ("dram__bytes_read+write of heavy_expand + heavy_rounds + sketch_kernel + heavy_topk, "
                 "one ncu capture at N=1 on the scale-22 matrix; null for other sizes and N")
 
