@@ -355,20 +355,30 @@ bool run_csg(Context &ctx, int32_t n, int32_t ncols, int32_t row_base, int32_t n
     if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
     if (!launch_sketch(ctx, n, nnz, p, d_ptr, s, row_base, zero_table)) return false;
   } else {
-    if (zero_table)
-      CSG_CUDA(cudaMemsetAsync(s.table, 0, sizeof(uint64_t) * static_cast<size_t>(n) * p.k, st));
-    if (!launch_priority_pick(ctx, n, nnz, p.chunk, d_ptr, s, sp, ahead_chunk_nnz)) return false;
-    CSG_CUDA(cudaEventRecord(ctx.ev[5], st));
-    CSG_CUDA(cudaStreamWaitEvent(ctx.side_stream, ctx.ev[5], 0));
-    // the chunk ahead: queued first, so that the host's launches of the rest do not delay it
-    if (!launch_transpose(ctx, n, ncols, nnz, p.chunk, d_ptr, d_ind, sp, false, PHASE_PRIO, s.ctrl)) return false;
-    if (!launch_sketch(ctx, n, nnz, p, d_ptr, sp, row_base, false, PHASE_PRIO)) return false;
-    CSG_CUDA(cudaEventRecord(ctx.ev[7], ctx.side_stream));
-    if (!launch_transpose(ctx, n, ncols, nnz, p.chunk, d_ptr, d_ind, s, false, PHASE_REST, sp.ctrl)) return false;
-    if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
-    CSG_CUDA(cudaStreamWaitEvent(st, ctx.ev[8], 0));
-    if (!launch_sketch(ctx, n, nnz, p, d_ptr, s, row_base, false, PHASE_REST)) return false;
-    CSG_CUDA(cudaStreamWaitEvent(st, ctx.ev[7], 0));
+    auto two_parts = [&]() -> bool {
+      if (zero_table)
+        CSG_CUDA(cudaMemsetAsync(s.table, 0, sizeof(uint64_t) * static_cast<size_t>(n) * p.k, st));
+      if (!launch_priority_pick(ctx, n, nnz, p.chunk, d_ptr, s, sp, ahead_chunk_nnz)) return false;
+      CSG_CUDA(cudaEventRecord(ctx.ev[5], st));
+      CSG_CUDA(cudaStreamWaitEvent(ctx.side_stream, ctx.ev[5], 0));
+      // the chunk ahead: queued first, so that the host's launches of the rest do not delay it
+      if (!launch_transpose(ctx, n, ncols, nnz, p.chunk, d_ptr, d_ind, sp, false, PHASE_PRIO, s.ctrl)) return false;
+      if (!launch_sketch(ctx, n, nnz, p, d_ptr, sp, row_base, false, PHASE_PRIO)) return false;
+      CSG_CUDA(cudaEventRecord(ctx.ev[7], ctx.side_stream));
+      if (!launch_transpose(ctx, n, ncols, nnz, p.chunk, d_ptr, d_ind, s, false, PHASE_REST, sp.ctrl)) return false;
+      if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[1], st));
+      CSG_CUDA(cudaStreamWaitEvent(st, ctx.ev[8], 0));
+      if (!launch_sketch(ctx, n, nnz, p, d_ptr, s, row_base, false, PHASE_REST)) return false;
+      CSG_CUDA(cudaStreamWaitEvent(st, ctx.ev[7], 0));
+      return true;
+    };
+    if (!two_parts()) {
+      // a launch failed with the second stream forked and not joined: nothing of this call
+      // may still be running when the next one reuses the workspace
+      cudaStreamSynchronize(ctx.side_stream);
+      cudaStreamSynchronize(st);
+      return false;
+    }
   }
   if (timing) CSG_CUDA(cudaEventRecord(ctx.ev[2], st));
   if (stats && !launch_table_stats(ctx, n, p.k, s.table, s.ctrl)) return false;
