@@ -38,7 +38,12 @@
 //    outcome can be read off the sketch as it stands, all lanes at once (see "the chains
 //    in rounds" below) - 16 elements per round on the longest R-MAT rows, at under half
 //    the cost of 16 sequential steps.  Larger sketches keep the element-wise chain
-//    (heavy_consume_kernel).
+//    (heavy_consume_kernel);
+//  * a large call runs in two parts (see run_csg): the chunk with the most nonzeros on a
+//    stream of its own, ahead of the rest.  Both parts go through launch_cells with their own
+//    lists and control words; their chain kernels have eight warps per block, and only the
+//    critical rows - those long enough to decide when the call ends - keep a scheduler to
+//    themselves.
 #include "common.cuh"
 
 namespace csg {
