@@ -1466,37 +1466,13 @@ __global__ void __launch_bounds__(32 * WARPS, 1) heavy_rounds_kernel(SketchArgs 
   // those chains have a scheduler each); the blocks behind them take the other rows eight at a
   // time, in list order, so that the rows fill as few SMs as they can and blocks without rows
   // leave at once.  Blocks of four warps draw tickets.
-  uint32_t item = 0, stride = 0, last = heavy;
-  if (WARPS > S_WARPS) {
-    uint32_t crit = a.ctrl[CTRL_CRITICAL_ROWS];
-    crit = crit < heavy ? crit : heavy;
-    uint32_t sparse_blocks = (crit + S_WARPS - 1) / S_WARPS;
-    if (sparse_blocks >= gridDim.x) {  // no block left for other rows: all rows alike
-      sparse_blocks = gridDim.x;
-      crit = heavy;
-    }
-    if (blockIdx.x < sparse_blocks) {
-      if (warp >= S_WARPS) return;
-      item = blockIdx.x * S_WARPS + warp;
-      stride = sparse_blocks * S_WARPS;
-      last = crit;
-    } else {
-      item = crit + (blockIdx.x - sparse_blocks) * WARPS + warp;
-      stride = (gridDim.x - sparse_blocks) * WARPS;
-    }
-  }
-  for (;; item += stride) {
-    if (WARPS == S_WARPS) {
-      if (lane == 0) item = atomicAdd(&a.ctrl[CTRL_HEAVY_TICKET + 1], 1u);
-      item = __shfl_sync(FULL, item, 0);
-    }
-    if (item >= last) break;
+  auto run_row = [&](uint32_t item) {
     const int32_t r = a.row_list[item];
     // checked build: the row, its place in the state array and its stream's extent
     if (!index_ok(a.ctrl, CHK_LIST, r, a.n) || !index_ok(a.ctrl, CHK_STATE, item, a.heavy_max) ||
         !index_ok(a.ctrl, CHK_STREAM, static_cast<long long>(a.heavy_off[item]) + a.row_work[r],
                   static_cast<long long>(a.stream_cap) + 1))
-      continue;
+      return;
     int32_t *out = a.heavy_state + static_cast<size_t>(item) * (2 * CELLS * 32);
 #ifdef CSG_ROUND_PROFILE
     const unsigned long long row_t0 = clock64();
@@ -1517,6 +1493,34 @@ __global__ void __launch_bounds__(32 * WARPS, 1) heavy_rounds_kernel(SketchArgs 
     (void)row_off;
     if (lane == 0) a.heavy_off[item] = static_cast<uint32_t>((clock64() - row_t0) >> 10);
 #endif
+  };
+  if constexpr (WARPS == S_WARPS) {
+    for (;;) {
+      uint32_t item = 0;
+      if (lane == 0) item = atomicAdd(&a.ctrl[CTRL_HEAVY_TICKET + 1], 1u);
+      item = __shfl_sync(FULL, item, 0);
+      if (item >= heavy) break;
+      run_row(item);
+    }
+  } else {
+    uint32_t crit = a.ctrl[CTRL_CRITICAL_ROWS];
+    crit = crit < heavy ? crit : heavy;
+    uint32_t sparse_blocks = (crit + S_WARPS - 1) / S_WARPS;
+    if (sparse_blocks >= gridDim.x) {  // no block left for other rows: all rows alike
+      sparse_blocks = gridDim.x;
+      crit = heavy;
+    }
+    uint32_t item, stride, last = heavy;
+    if (blockIdx.x < sparse_blocks) {
+      if (warp >= S_WARPS) return;
+      item = blockIdx.x * S_WARPS + warp;
+      stride = sparse_blocks * S_WARPS;
+      last = crit;
+    } else {
+      item = crit + (blockIdx.x - sparse_blocks) * WARPS + warp;
+      stride = (gridDim.x - sparse_blocks) * WARPS;
+    }
+    for (; item < last; item += stride) run_row(item);
   }
 }
 
