@@ -595,6 +595,28 @@ def test_shard_must_hold_whole_chunks():
     assert np.array_equal(order.cpu().numpy(), oracle.csg(ptr, ind, False)[3072:])
 
 
+@pytest.mark.parametrize("name", ["rmat16", "dense_ragged", "bigchunk"])
+def test_row_shards_that_run_one_chunk_ahead(name):
+    # the shards of a multi-GPU run, one after the other on this GPU, each forced onto the
+    # route that runs its heaviest chunk ahead: together they are the single-GPU permutation
+    sp = _sp()
+    from chunkedgreedy_b200 import dist as csgdist
+    ptr, ind, val, sym, params = cases.build(name)
+    n = ptr.size - 1
+    chunk = params.get("chunk_size", 0) or 1024
+    k = params.get("k", 0) or csgdist.resolve_k(n, ind.size, 0)
+    want = oracle.csg(ptr, ind, False, **params)
+    ctx = sp.Context()
+    ctx.set_ahead_threshold(1)
+    parts = []
+    for r0, r1 in csgdist.shard_bounds(ptr, chunk, 3):
+        pl, il = csgdist.extract_shard(ptr, ind, r0, r1)
+        kw = {key: v for key, v in params.items() if key not in ("k", "chunk_size")}
+        parts.append(csgdist.csg_shard(_dev(pl), _dev(il), n, r0, k=k, chunk_size=chunk, ctx=ctx, **kw).cpu().numpy())
+    assert np.array_equal(np.concatenate(parts), want)
+    ctx.close()
+
+
 def test_spmm_of_a_row_block_against_the_whole_product():
     # the row-partitioned product: a block of rows times the whole dense operand
     sp = _sp()
