@@ -348,47 +348,65 @@ __global__ void __launch_bounds__(1024) pick_priority_kernel(TransposeArgs a, Tr
 }
 
 // Work list of the chunk ahead: its rows that stream 65,536 candidates or more (the other
-// rows of the chunk go with everybody else's).  First the critical rows - at least half as
-// long as the longest, the ones that can decide when the call ends; their chains keep a
-// scheduler to themselves - then the others, heaviest bucket first.  One block.
+// rows of the chunk go with everybody else's), longest stream first, so that the eight rows a
+// block of the chain kernel takes are of a length and the block is done when they are.  The
+// critical rows - at least half as long as the longest, the ones that can decide when the call
+// ends; their chains keep a scheduler to themselves - are then the head of the list.  One block;
+// a chunk has at most PRIO_MAX_CHUNK rows.
+constexpr int PRIO_MAX_CHUNK = 4096;
 __global__ void __launch_bounds__(1024) priority_rows_kernel(TransposeArgs ap, int32_t *row_list) {
-  __shared__ uint32_t count, longest, critical;
+  __shared__ int32_t s_row[PRIO_MAX_CHUNK];
+  __shared__ uint32_t s_work[PRIO_MAX_CHUNK];
+  __shared__ uint32_t count, critical;
   __shared__ unsigned long long need;
   if (threadIdx.x == 0) {
     count = 0;
     need = 0;
-    longest = 0;
     critical = 0;
   }
   __syncthreads();
   const uint32_t prio = ap.ctrl[CTRL_PRIO];
-  if (prio != PRIO_NONE) {
+  uint32_t longest = 0;
+  if (prio != PRIO_NONE && ap.chunk <= PRIO_MAX_CHUNK) {
     const int64_t start = static_cast<int64_t>(prio) * ap.chunk;
     const int64_t end = start + ap.chunk < ap.n ? start + ap.chunk : ap.n;
-    for (int64_t r = start + threadIdx.x; r < end; r += blockDim.x) atomicMax(&longest, ap.row_work[r]);
-    __syncthreads();
-    uint32_t bar = longest - longest / 2;
-    if (bar < (1u << (SKETCH_HEAVY_BUCKET - 1))) bar = 1u << (SKETCH_HEAVY_BUCKET - 1);
     for (int64_t r = start + threadIdx.x; r < end; r += blockDim.x) {
       const uint32_t t = ap.row_work[r];
-      if (t >= bar) {
-        row_list[atomicAdd(&count, 1u)] = static_cast<int32_t>(r);
+      if (t >= (1u << (SKETCH_HEAVY_BUCKET - 1))) {
+        const uint32_t at = atomicAdd(&count, 1u);
+        s_row[at] = static_cast<int32_t>(r);
+        s_work[at] = t;
         atomicAdd(&need, static_cast<unsigned long long>(t));
       }
     }
     __syncthreads();
-    if (threadIdx.x == 0) critical = count;
-    __syncthreads();
-    for (int b = 32; b >= SKETCH_HEAVY_BUCKET; --b) {
-      for (int64_t r = start + threadIdx.x; r < end; r += blockDim.x) {
-        const uint32_t t = ap.row_work[r];
-        if (t && t < bar && 32 - __clz(t) == b) {
-          row_list[atomicAdd(&count, 1u)] = static_cast<int32_t>(r);
-          atomicAdd(&need, static_cast<unsigned long long>(t));
-        }
+    const uint32_t H = count;
+    // place of every row in the order (longer stream first, then smaller row id)
+    for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) {
+      const uint32_t w = s_work[i];
+      const int32_t r = s_row[i];
+      uint32_t before = 0;
+      for (uint32_t j = 0; j < H; ++j) {
+        const uint32_t wj = s_work[j];
+        before += (wj > w || (wj == w && s_row[j] < r)) ? 1u : 0u;
       }
-      __syncthreads();
+      row_list[before] = r;
+      if (before == 0) longest = w;
     }
+    // (the thread that placed the first row knows the longest stream)
+    const uint32_t top = __reduce_max_sync(FULL, longest);
+    if ((threadIdx.x & 31) == 0 && top) atomicMax(&critical, top);  // borrowed as a maximum for a moment
+    __syncthreads();
+    longest = critical;
+    __syncthreads();
+    if (threadIdx.x == 0) critical = 0;
+    __syncthreads();
+    const uint32_t bar = longest - longest / 2;
+    uint32_t mine = 0;
+    for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) mine += s_work[i] >= bar ? 1u : 0u;
+    mine = __reduce_add_sync(FULL, mine);
+    if ((threadIdx.x & 31) == 0 && mine) atomicAdd(&critical, mine);
+    __syncthreads();
   }
   if (threadIdx.x == 0) {
     ap.ctrl[CTRL_ROWS_LISTED] = count;
